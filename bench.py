@@ -1,0 +1,532 @@
+#!/usr/bin/env python
+"""Benchmark of the inductor_x_b200 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  The headline workload (default) is the softmax -> LayerNorm chain on
+x[16384, 4096] bf16; one "step" is one pass of the fused kernel over that batch.  `value`
+is algorithmic HBM GB/s with inputs resident in HBM; `e2e` is the same metric through the
+public op with host buffers (pinned H2D of the inputs and D2H of the result inside the
+timed region).  With N > 1 (launched by torch.distributed.run) every rank runs the same
+per-GPU batch (rows sharded, weak scaling, no data-path collective) and the time is the
+max over ranks.
+
+`--impl reference` times the reference's ground truth for this graph - eager PyTorch on
+the host cores - on a bounded sample of the same workload (the reference itself needs an
+Ascend NPU stack and cannot execute here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Polls NVML (read-only) for SM clock and throttle reasons while the bench runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+        self.ok = False
+
+    def run(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+            while not self.stop_flag.is_set():
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                try:
+                    reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    reasons = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+                time.sleep(0.002)
+        except Exception:
+            self.ok = False
+
+    def summary(self, t0: float, t1: float):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        inside = [(m, r) for (t, m, r) in self.samples if t0 <= t <= t1] or \
+                 [(m, r) for (_, m, r) in self.samples[-3:]]
+        mhz = sorted(m for m, _ in inside)
+        bits = 0
+        for _, r in inside:
+            bits |= r
+        names = [n for b, n in self.REASONS.items() if bits & b]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": names, "samples": len(inside)}
+
+
+# ------------------------------------------------------------------------ workloads
+class SoftmaxLayerNorm:
+    """configs[1]: y = layer_norm(softmax(x,-1)*g + x) on x[16384,4096] bf16."""
+
+    name = "softmax_layernorm_bf16_16384x4096"
+    dtype = "bf16"
+    rows, cols = 16384, 4096
+
+    def algorithmic_bytes(self):
+        return 2 * self.rows * self.cols * 2 + 3 * self.cols * 2  # 268,460,032
+
+    def load_host(self, seed):
+        from oracle import inputs  # input generator only (seeded synthetic data)
+
+        self.host = inputs.c2(self.rows, self.cols, seed=seed)
+        return self.host
+
+    def setup(self, device, seed, n_sets=4):
+        d = self.load_host(seed)
+        self.params = [d[k].to(device) for k in ("g", "gamma", "beta")]
+        x = d["x"].to(device)
+        # distinct buffers per step: a step streams 268 MB (> 126 MB L2) and the next step
+        # touches different addresses, so nothing is served from cache
+        self.xs = [x] + [x.clone() for _ in range(n_sets - 1)]
+        self.ys = [torch.empty_like(x) for _ in range(n_sets)]
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        k = i % len(self.xs)
+        ops.softmax_layernorm(self.xs[k], *self.params, 1e-5, out=self.ys[k])
+        return 1  # kernels launched
+
+    def e2e_setup(self, device):
+        self.h_x = self.host["x"].pin_memory()
+        self.h_y = torch.empty_like(self.h_x).pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+        self.d_y = torch.empty_like(self.xs[0])
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        ops.softmax_layernorm(self.d_x, *self.params, 1e-5, out=self.d_y)
+        self.h_y.copy_(self.d_y, non_blocking=True)
+        return self.h_x.numel() * 2, self.h_y.numel() * 2
+
+    def cpu_sample(self, rows=1024):
+        from oracle import graphs
+
+        d = self.host
+        x = d["x"][:rows].contiguous()
+        fn = lambda: graphs.eager_softmax_layernorm(x, d["g"], d["gamma"], d["beta"], 1e-5)
+        nbytes = 2 * rows * self.cols * 2 + 3 * self.cols * 2
+        return fn, nbytes, f"{rows} of {self.rows} rows, eager PyTorch ops"
+
+
+class AffineGeluRowSum:
+    """configs[0]: out = sum(gelu(x*w+b), -1) on x[8192,1024] fp32."""
+
+    name = "affine_gelu_rowsum_f32_8192x1024"
+    dtype = "f32"
+    rows, cols = 8192, 1024
+
+    def algorithmic_bytes(self):
+        return self.rows * self.cols * 4 + 2 * self.cols * 4 + self.rows * 4  # 33,595,392
+
+    def load_host(self, seed):
+        from oracle import inputs
+
+        self.host = inputs.c1(self.rows, self.cols, seed=seed)
+        return self.host
+
+    def setup(self, device, seed, n_sets=8):
+        d = self.load_host(seed)
+        self.w, self.b = d["w"].to(device), d["b"].to(device)
+        x = d["x"].to(device)
+        # 32 MiB fits in L2: rotate over 8 copies (256 MiB) so every step reads from HBM
+        self.xs = [x] + [x.clone() for _ in range(n_sets - 1)]
+        self.out = torch.empty(self.rows, device=device)
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        ops.affine_gelu_rowsum(self.xs[i % len(self.xs)], self.w, self.b, out=self.out)
+        return 1
+
+    def e2e_setup(self, device):
+        self.h_x = self.host["x"].pin_memory()
+        self.h_o = torch.empty(self.rows).pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        ops.affine_gelu_rowsum(self.d_x, self.w, self.b, out=self.out)
+        self.h_o.copy_(self.out, non_blocking=True)
+        return self.h_x.numel() * 4, self.rows * 4
+
+    def cpu_sample(self, rows=8192):
+        import torch.nn.functional as F
+
+        d = self.host
+        x = d["x"][:rows]
+        fn = lambda: F.gelu(x * d["w"] + d["b"]).sum(-1)
+        return fn, rows * self.cols * 4 + 2 * self.cols * 4 + rows * 4, f"{rows} of {self.rows} rows, eager PyTorch ops"
+
+
+class PermutedAmax:
+    """configs[2] part 1: amax over dim 1 of x[64,128,256,64].permute(0,2,1,3), fp16."""
+
+    name = "permuted_amax_f16_64x128x256x64"
+    dtype = "f16"
+    shape = (64, 128, 256, 64)
+
+    def algorithmic_bytes(self):
+        a, b, c, d = self.shape
+        return a * b * c * d * 2 + a * b * d * 2  # 269,484,032
+
+    def load_host(self, seed):
+        from oracle import inputs
+
+        self.host = inputs.c3a(self.shape, seed=seed)["x"]
+        return self.host
+
+    def setup(self, device, seed, n_sets=3):
+        x = self.load_host(seed)
+        xd = x.to(device)
+        self.xs = [xd] + [xd.clone() for _ in range(n_sets - 1)]
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        a, b, c, d = self.shape
+        self.out = ops.outer_reduce(self.xs[i % len(self.xs)].view(a * b, c, d), "amax", rsplit=1)
+        return 1
+
+    def e2e_setup(self, device):
+        self.h_x = self.host.pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+        a, b, c, d = self.shape
+        self.h_o = torch.empty(a * b, d, dtype=torch.float16).pin_memory()
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        a, b, c, d = self.shape
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        o = ops.outer_reduce(self.d_x.view(a * b, c, d), "amax", rsplit=1)
+        self.h_o.copy_(o, non_blocking=True)
+        return self.h_x.numel() * 2, self.h_o.numel() * 2
+
+    def cpu_sample(self, slabs=8):
+        x = self.host[:slabs]
+        fn = lambda: x.permute(0, 2, 1, 3).amax(1)
+        _, b, c, d = self.shape
+        return fn, slabs * b * c * d * 2 + slabs * b * d * 2, f"{slabs} of {self.shape[0]} outer slabs, eager PyTorch"
+
+
+class PermutedSum(PermutedAmax):
+    """configs[2] part 2: sum over dim 3 of the same permuted view -> [64,256,128]."""
+
+    name = "permuted_sum_f16_64x128x256x64"
+
+    def algorithmic_bytes(self):
+        a, b, c, d = self.shape
+        return a * b * c * d * 2 + a * b * c * 2  # 272,629,760
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        a, b, c, d = self.shape
+        self.out = ops.short_row_reduce(self.xs[i % len(self.xs)], "sum", (c * b, 1, b))
+        return 1
+
+    def e2e_setup(self, device):
+        self.h_x = self.host.pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+        a, b, c, d = self.shape
+        self.h_o = torch.empty(a * b * c, dtype=torch.float16).pin_memory()
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        a, b, c, d = self.shape
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        o = ops.short_row_reduce(self.d_x, "sum", (c * b, 1, b))
+        self.h_o.copy_(o, non_blocking=True)
+        return self.h_x.numel() * 2, self.h_o.numel() * 2
+
+    def cpu_sample(self, slabs=8):
+        x = self.host[:slabs]
+        fn = lambda: x.permute(0, 2, 1, 3).sum(3)
+        _, b, c, d = self.shape
+        return fn, slabs * b * c * d * 2 + slabs * b * c * 2, f"{slabs} of {self.shape[0]} outer slabs, eager PyTorch"
+
+
+class IndexSelect:
+    """configs[2] part 3: index_select of 262144 rows from a [2^20,128] fp16 table."""
+
+    name = "index_select_f16_1Mx128_262144"
+    dtype = "u8"  # bytes are moved, not computed on
+    n_rows, dim, n_idx = 1 << 20, 128, 262144
+
+    def algorithmic_bytes(self):
+        return self.n_idx * 8 + 2 * self.n_idx * self.dim * 2  # 136,314,880
+
+    def load_host(self, seed):
+        from oracle import inputs
+
+        self.host = inputs.c3b(self.n_rows, self.dim, self.n_idx, seed=seed)
+        return self.host
+
+    def setup(self, device, seed, n_sets=4):
+        d = self.load_host(seed)
+        self.table = d["table"].to(device)  # 256 MiB: larger than L2
+        g = torch.Generator().manual_seed(seed + 1000)
+        # different random index sets per step so rows are not L2-resident from the last step
+        self.idxs = [d["idx"].to(device)] + [
+            torch.randint(0, self.n_rows, (self.n_idx,), generator=g).to(device) for _ in range(n_sets - 1)]
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        self.out = ops.index_select_rows(self.table, self.idxs[i % len(self.idxs)], check_bounds=False)
+        return 1
+
+    def e2e_setup(self, device):
+        self.h_idx = self.host["idx"].pin_memory()
+        self.d_idx = torch.empty_like(self.idxs[0])
+        self.h_o = torch.empty(self.n_idx, self.dim, dtype=torch.float16).pin_memory()
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        self.d_idx.copy_(self.h_idx, non_blocking=True)
+        o = ops.index_select_rows(self.table, self.d_idx, check_bounds=False)
+        self.h_o.copy_(o, non_blocking=True)
+        return self.n_idx * 8, self.h_o.numel() * 2
+
+    def cpu_sample(self):
+        d = self.host
+        fn = lambda: d["table"].index_select(0, d["idx"])
+        return fn, self.algorithmic_bytes(), "full workload, torch.index_select on CPU"
+
+
+WORKLOADS = {
+    "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
+    "c3a_sum": PermutedSum, "c3b": IndexSelect,
+}
+
+
+# ---------------------------------------------------------------------------- driver
+def time_cpu(fn, min_seconds=2.0, max_iters=50):
+    fn()
+    fn()
+    best, total, it = float("inf"), 0.0, 0
+    while (total < min_seconds or it < 5) and it < max_iters:
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+        total += dt
+        it += 1
+    return best
+
+
+def run_reference(args, wl_cls):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    wl = wl_cls()
+    wl.load_host(0)  # host data only; no GPU is touched on this arm
+    fn, nbytes, sample = wl.cpu_sample()
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = nbytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "fused-kernel HBM GB/s", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic",
+        "config": {"workload": wl.name, "note": "eager PyTorch on host cores; the reference's own "
+                   "ground truth (it asserts compiled == eager) - the reference itself needs an Ascend NPU"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl_cls = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, wl_cls)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from inductor_x_b200 import runtime as rt
+
+    rt.load()
+    peaks = measured_peaks()
+    wl = wl_cls()
+    wl.setup(device, seed=rank)  # each rank owns a different shard of the global batch
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        wl.step(i)
+    barrier()
+
+    # ---- timed region: exactly K steps, CUDA events on the launching (current) stream
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    launches = 0
+    t_wall0 = time.perf_counter()
+    whole0 = torch.cuda.Event(enable_timing=True)
+    whole1 = torch.cuda.Event(enable_timing=True)
+    whole0.record()
+    for i in range(args.steps):
+        starts[i].record()
+        launches += wl.step(i)
+        ends[i].record()
+    whole1.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    total_ms = whole0.elapsed_time(whole1)
+    kernel_ms = sorted(s.elapsed_time(e) for s, e in zip(starts, ends))
+    avg_kernel_ms = sum(kernel_ms) / len(kernel_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    nbytes = wl.algorithmic_bytes()
+    value = world * nbytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public op with host buffers
+    wl.e2e_setup(device)
+    for _ in range(2):
+        wl.e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        h2d, d2h = wl.e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * nbytes / (e2e_ms / args.e2e_steps * 1e-3) / 1e9
+
+    if rank == 0:
+        sampler.stop_flag.set()
+        sampler.join(timeout=2)
+        clocks = sampler.summary(t_wall0, t_wall1)
+
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
+            fn, cbytes, sample = wl.cpu_sample()
+            best = time_cpu(fn)
+            cpu = {"value": cbytes / best / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+                   "kind": "port", "sample": sample + f"; best of >=5, {best * 1e3:.2f} ms"}
+
+        achieved = nbytes / (avg_kernel_ms * 1e-3) / 1e9
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                traffic = json.load(f).get(wl.name)
+        line = {
+            "metric": "fused-kernel HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic",
+            "config": {"workload": wl.name, "algorithmic_bytes_per_step": nbytes,
+                       "l2": "working set per step exceeds the 126 MB L2 and steps rotate over "
+                             f"{len(getattr(wl, 'xs', getattr(wl, 'idxs', [0])))} distinct buffer sets",
+                       "sharding": f"rows split over {world} GPU(s), no collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+                         "peak_source": peaks["source"], "kernel_ms_avg": avg_kernel_ms,
+                         "kernel_ms_median": kernel_ms[len(kernel_ms) // 2],
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,239 @@
+// Device-side building blocks shared by every kernel template of the B200 backend:
+// 128-bit vector access, dtype packing, warp / team reductions and the math used by
+// the pre-instantiated functors.  Header-only so that generated functor modules can
+// include the same code as the prebuilt library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <float.h>
+
+namespace ixb {
+
+using bf16 = __nv_bfloat16;
+using f16 = __half;
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ---------------------------------------------------------------------------------
+// Element traits: how many elements one 128-bit vector holds and how to widen /
+// narrow them.  Half types are always computed in fp32 (the reference upcasts every
+// half load, inductor_x/codegen/triton.py:1431-1433).
+// ---------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static constexpr int kVec = 4;
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Elem<f16> {
+  static constexpr int kVec = 8;
+  static __device__ __forceinline__ float to_f(f16 v) { return __half2float(v); }
+  static __device__ __forceinline__ f16 from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<bf16> {
+  static constexpr int kVec = 8;
+  static __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ bf16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// 128-bit global access.  Inputs that are read once stream through L1 without
+// allocating; outputs use a streaming store so they do not evict reusable lines.
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint4 ldg_keep(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void stg_stream(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// Widen one 128-bit vector into fp32 lanes.
+template <typename T> __device__ __forceinline__ void unpack(const uint4& raw, float* out);
+template <> __device__ __forceinline__ void unpack<float>(const uint4& raw, float* out) {
+  out[0] = __uint_as_float(raw.x);
+  out[1] = __uint_as_float(raw.y);
+  out[2] = __uint_as_float(raw.z);
+  out[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void unpack<bf16>(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void unpack<f16>(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+// Narrow fp32 lanes into one 128-bit vector (round to nearest even).
+template <typename T> __device__ __forceinline__ uint4 pack(const float* in);
+template <> __device__ __forceinline__ uint4 pack<float>(const float* in) {
+  return make_uint4(__float_as_uint(in[0]), __float_as_uint(in[1]), __float_as_uint(in[2]),
+                    __float_as_uint(in[3]));
+}
+template <> __device__ __forceinline__ uint4 pack<bf16>(const float* in) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <> __device__ __forceinline__ uint4 pack<f16>(const float* in) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---------------------------------------------------------------------------------
+// Reduction operators.  `combine` must be associative and commutative.
+// ---------------------------------------------------------------------------------
+struct SumOp {
+  static __device__ __forceinline__ float identity() { return 0.f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return a + b; }
+};
+// max / min propagate NaN like torch.amax / torch.amin.
+struct MaxOp {
+  static __device__ __forceinline__ float identity() { return -INFINITY; }
+  static __device__ __forceinline__ float combine(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+};
+struct MinOp {
+  static __device__ __forceinline__ float identity() { return INFINITY; }
+  static __device__ __forceinline__ float combine(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+};
+// Non-propagating max for values known to be finite (softmax row maximum).
+struct FastMaxOp {
+  static __device__ __forceinline__ float identity() { return -INFINITY; }
+  static __device__ __forceinline__ float combine(float a, float b) { return fmaxf(a, b); }
+};
+struct ProdOp {
+  static __device__ __forceinline__ float identity() { return 1.f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return a * b; }
+};
+
+template <class Op> __device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = Op::combine(v, __shfl_xor_sync(kFull, v, o));
+  return v;
+}
+// Reduce within aligned groups of WIDTH lanes (WIDTH a power of two <= 32).
+template <class Op, int WIDTH> __device__ __forceinline__ float lane_group_reduce(float v) {
+#pragma unroll
+  for (int o = WIDTH / 2; o > 0; o >>= 1) v = Op::combine(v, __shfl_xor_sync(kFull, v, o));
+  return v;
+}
+
+// (value, index) pair for arg-reductions.  Ties resolve to the smaller index and a NaN
+// value wins over any number, matching torch.argmax / torch.argmin.
+struct ArgPair {
+  float v;
+  long long i;
+};
+template <bool IS_MAX> struct ArgOp {
+  static __device__ __forceinline__ ArgPair identity() {
+    return ArgPair{IS_MAX ? -INFINITY : INFINITY, 0x7fffffffffffffffLL};
+  }
+  static __device__ __forceinline__ ArgPair combine(ArgPair a, ArgPair b) {
+    const bool a_nan = a.v != a.v, b_nan = b.v != b.v;
+    bool take_b;
+    if (a_nan || b_nan) {
+      take_b = b_nan && (!a_nan || b.i < a.i);
+    } else if (a.v == b.v) {
+      take_b = b.i < a.i;
+    } else {
+      take_b = IS_MAX ? (b.v > a.v) : (b.v < a.v);
+    }
+    return take_b ? b : a;
+  }
+};
+template <bool IS_MAX> __device__ __forceinline__ ArgPair warp_reduce_arg(ArgPair p) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair q;
+    q.v = __shfl_xor_sync(kFull, p.v, o);
+    q.i = __shfl_xor_sync(kFull, p.i, o);
+    p = ArgOp<IS_MAX>::combine(p, q);
+  }
+  return p;
+}
+
+// Named barrier over `nthreads` threads (a multiple of 32); id 0 is __syncthreads().
+__device__ __forceinline__ void team_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------
+// Math used by the pre-instantiated functors.
+// ---------------------------------------------------------------------------------
+// exact-erf GELU, the default of torch.nn.functional.gelu.
+__device__ __forceinline__ float gelu_erf(float v) {
+  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+}
+__device__ __forceinline__ float fast_exp2(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Packed fp32x2 arithmetic (one issue slot for two lanes on sm_100).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<const unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<const unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+  return d;
+}
+
+}  // namespace ixb

@@ -1,0 +1,185 @@
+"""Tensor-level entry points over the C ABI: one function per prebuilt kernel family.
+
+These are what the generated wrapper code, the tests and ``bench.py`` call.  Each takes
+CUDA tensors, validates layout, allocates the output with torch (plumbing only) and
+enqueues exactly the native kernels on the current stream.  A CPU tensor is rejected:
+there is no host path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import runtime as rt
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("inductor_x_b200 kernels take CUDA tensors only (no CPU path)")
+
+
+def _cfg_ref(cfg):
+    c = rt.make_cfg(cfg)
+    return (ctypes.byref(c) if c is not None else None), c
+
+
+def affine_gelu_rowsum(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, *, out=None, cfg=None):
+    """``sum(gelu(x * w + b), dim=-1)`` for fp32 ``x[rows, cols]``, ``w[cols]``, ``b[cols]``."""
+    _need_cuda(x, w, b)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous fp32 matrix")
+    rows, cols = x.shape
+    if w.shape != (cols,) or b.shape != (cols,) or w.dtype != x.dtype or b.dtype != x.dtype:
+        raise ValueError("w and b must be fp32 vectors of length cols")
+    w, b = w.contiguous(), b.contiguous()
+    if out is None:
+        out = torch.empty(rows, dtype=x.dtype, device=x.device)
+    ref, keep = _cfg_ref(cfg)
+    rt.check("ixb_affine_gelu_rowsum_f32", rt.load().ixb_affine_gelu_rowsum_f32(
+        x.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(), rows, cols, ref,
+        rt.raw_stream(x.device)))
+    return out
+
+
+def softmax_layernorm(x, g, gamma, beta, eps: float = 1e-5, *, out=None, cfg=None):
+    """``layer_norm(softmax(x, -1) * g + x, [cols], gamma, beta, eps)`` in one pass."""
+    _need_cuda(x, g, gamma, beta)
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    if not x.is_contiguous() or x.dim() < 1:
+        raise ValueError("x must be contiguous")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    for name, v in (("g", g), ("gamma", gamma), ("beta", beta)):
+        if v.shape != (cols,) or v.dtype != x.dtype:
+            raise ValueError(f"{name} must have shape ({cols},) and dtype {x.dtype}")
+    g, gamma, beta = g.contiguous(), gamma.contiguous(), beta.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    ref, keep = _cfg_ref(cfg)
+    rt.check("ixb_softmax_layernorm", rt.load().ixb_softmax_layernorm(
+        rt.DTYPE_CODE[x.dtype], x.data_ptr(), g.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+        out.data_ptr(), rows, cols, float(eps), ref, rt.raw_stream(x.device)))
+    return out
+
+
+def rmsnorm(x, w, eps: float = 1e-6, *, residual=None, return_residual: bool = False, cfg=None):
+    """RMSNorm over the last axis with an optional fused residual add.
+
+    Returns ``y`` or ``(y, h)`` where ``h = x + residual`` (rounded to the storage dtype)."""
+    _need_cuda(x, w, residual)
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    if w.shape != (cols,) or w.dtype != x.dtype:
+        raise ValueError("w must be a vector of length cols in x's dtype")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype
+                                 or not residual.is_contiguous()):
+        raise ValueError("residual must match x")
+    y = torch.empty_like(x)
+    h = torch.empty_like(x) if (residual is not None and return_residual) else None
+    ref, keep = _cfg_ref(cfg)
+    rt.check("ixb_rmsnorm", rt.load().ixb_rmsnorm(
+        rt.DTYPE_CODE[x.dtype], x.data_ptr(), rt.ptr(residual), w.contiguous().data_ptr(),
+        y.data_ptr(), rt.ptr(h), rows, cols, float(eps), ref, rt.raw_stream(x.device)))
+    return (y, h) if h is not None else y
+
+
+def row_reduce(x: torch.Tensor, kind: str, *, correction: float = 1.0, cfg=None):
+    """Reduce the last axis of contiguous ``x``.  ``kind``: sum, mean, amax, amin, argmax,
+    argmin or var_mean (returns ``(var, mean)``)."""
+    _need_cuda(x)
+    if not x.is_contiguous() or x.dim() < 1:
+        raise ValueError("x must be contiguous")
+    code = rt.REDUCE_CODE[kind]
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    lead = x.shape[:-1]
+    out_dtype = torch.int64 if code in (rt.IXB_ARGMAX, rt.IXB_ARGMIN) else x.dtype
+    out = torch.empty(lead, dtype=out_dtype, device=x.device)
+    out2 = torch.empty(lead, dtype=x.dtype, device=x.device) if code == rt.IXB_VAR_MEAN else None
+    ref, keep = _cfg_ref(cfg)
+    rt.check("ixb_row_reduce", rt.load().ixb_row_reduce(
+        rt.DTYPE_CODE[x.dtype], code, x.data_ptr(), out.data_ptr(), rt.ptr(out2), rows, cols,
+        float(correction), ref, rt.raw_stream(x.device)))
+    return (out, out2) if out2 is not None else out
+
+
+def outer_reduce(x: torch.Tensor, kind: str, *, rsplit: int = 0, scratch: Optional[torch.Tensor] = None):
+    """Reduce the middle axis of contiguous ``x[outer, R, inner]`` -> ``[outer, inner]``.
+
+    ``rsplit`` > 1 forces a split of the reduced axis (0 = library's choice); the fp32
+    scratch it needs is taken from ``scratch`` or allocated here with torch."""
+    _need_cuda(x, scratch)
+    if x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous [outer, R, inner] tensor")
+    outer, R, inner = x.shape
+    code = rt.REDUCE_CODE[kind]
+    lib = rt.load()
+    if rsplit <= 0 and outer and inner:
+        rsplit = rt.choose_config(rt.IXB_FAM_OUTER, x.dtype, outer, R, inner).rsplit
+    need = lib.ixb_outer_reduce_scratch_bytes(outer, inner, rsplit)
+    if need and (scratch is None or scratch.numel() * scratch.element_size() < need):
+        scratch = torch.empty(need // 4, dtype=torch.float32, device=x.device)
+    out = torch.empty((outer, inner), dtype=x.dtype, device=x.device)
+    cfg = rt.IxbCfg(rsplit=max(rsplit, 1))
+    sbytes = scratch.numel() * scratch.element_size() if scratch is not None else 0
+    rt.check("ixb_outer_reduce", lib.ixb_outer_reduce(
+        rt.DTYPE_CODE[x.dtype], code, x.data_ptr(), out.data_ptr(), outer, R, inner, rt.ptr(scratch),
+        sbytes, ctypes.byref(cfg), rt.raw_stream(x.device)))
+    return out
+
+
+def short_row_reduce(x: torch.Tensor, kind: str, out_strides: Sequence[int],
+                     out: Optional[torch.Tensor] = None):
+    """Reduce the short stride-1 axis of contiguous ``x[A, B, C, L]`` and store result
+    ``(a, b, c)`` at element offset ``a*sa + b*sb + c*sc`` of ``out``."""
+    _need_cuda(x, out)
+    if x.dim() != 4 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous [A, B, C, L] tensor")
+    A, B, C, L = x.shape
+    sa, sb, sc = (int(s) for s in out_strides)
+    if out is None:
+        out = torch.empty(A * B * C, dtype=x.dtype, device=x.device)
+    rt.check("ixb_short_row_reduce", rt.load().ixb_short_row_reduce(
+        rt.DTYPE_CODE[x.dtype], rt.REDUCE_CODE[kind], x.data_ptr(), out.data_ptr(), A, B, C, L,
+        sa, sb, sc, rt.raw_stream(x.device)))
+    return out
+
+
+def index_select_rows(table: torch.Tensor, idx: torch.Tensor, *, wrap_negative: bool = False,
+                      check_bounds: bool = True):
+    """``table.index_select(0, idx)`` for a 2-D+ table whose rows are contiguous.
+
+    With ``check_bounds`` an out-of-range index raises ``IndexError`` (this reads a device
+    status word back, i.e. synchronises; pass False inside latency-critical code)."""
+    _need_cuda(table, idx)
+    if table.dim() < 1 or idx.dim() != 1 or idx.dtype not in (torch.int64, torch.int32):
+        raise ValueError("table must have >= 1 dim, idx must be a 1-D int32/int64 tensor")
+    n_rows = table.shape[0]
+    row_shape = table.shape[1:]
+    if table.dim() > 1 and not table[0].is_contiguous():
+        raise ValueError("rows of table must be contiguous")
+    row_elems = 1
+    for s in row_shape:
+        row_elems *= s
+    row_bytes = row_elems * table.element_size()
+    pitch = (table.stride(0) if table.dim() > 1 else 1) * table.element_size()
+    if n_rows <= 1:
+        pitch = max(pitch, row_bytes)
+    idx = idx.contiguous()
+    m = idx.numel()
+    out = torch.empty((m, *row_shape), dtype=table.dtype, device=table.device)
+    status = torch.zeros(2, dtype=torch.int32, device=table.device) if check_bounds else None
+    rt.check("ixb_index_select_rows", rt.load().ixb_index_select_rows(
+        table.data_ptr(), idx.data_ptr(), out.data_ptr(), n_rows, m, row_bytes, pitch,
+        rt.DTYPE_CODE[idx.dtype], int(wrap_negative), rt.ptr(status), rt.raw_stream(table.device)))
+    if status is not None:
+        flag, pos = status.tolist()
+        if flag:
+            raise IndexError(f"index_select_rows: index out of range at position {pos}")
+    return out
