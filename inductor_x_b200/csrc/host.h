@@ -35,12 +35,15 @@ bool choose_row(int64_t cols, int elsize, int max_vpt, ixb_cfg* cfg);
 // Dispatch over the instantiated (TEAM, VPT) pairs of the row template.  TEAMS is
 // derived: CTAs are 256 threads unless a single team is larger.
 #define IXB_ROW_TEAMS(TEAM_) ((TEAM_) >= 256 ? 1 : 256 / (TEAM_))
+// Register budget: CTAs of 256 threads are compiled for two resident CTAs per SM (at
+// most 128 registers per thread), which measured fastest for the fused bodies; larger
+// CTAs take what they need.
+#define IXB_ROW_MIN_CTAS(TEAM_) ((TEAM_) <= 256 ? 2 : 1)
 #define IXB_ROW_CASE(BODY, TEAM_, VPT_, AL_)                                                    \
   if (cfg.team == (TEAM_) && cfg.vpt == (VPT_))                                                 \
     return ixb_host::cuda_status(                                                               \
-        ixb::launch_row<BODY, TEAM_, IXB_ROW_TEAMS(TEAM_), VPT_, AL_>(p, rows, (int)cols,       \
-                                                                      dev->sm_count, cfg.grid,  \
-                                                                      (cudaStream_t)stream));
+        ixb::launch_row<BODY, TEAM_, IXB_ROW_TEAMS(TEAM_), VPT_, AL_, IXB_ROW_MIN_CTAS(TEAM_)>( \
+            p, rows, (int)cols, dev->sm_count, cfg.grid, (cudaStream_t)stream));
 #define IXB_ROW_DISPATCH(BODY, AL_) \
   IXB_ROW_CASE(BODY, 32, 1, AL_)    \
   IXB_ROW_CASE(BODY, 32, 2, AL_)    \

@@ -188,6 +188,19 @@ template <bool IS_MAX> __device__ __forceinline__ ArgPair warp_reduce_arg(ArgPai
   return p;
 }
 
+// Warp-wide maximum in one instruction (sm_100a redux on fp32).
+__device__ __forceinline__ float warp_max_fast(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // Named barrier over `nthreads` threads (a multiple of 32); id 0 is __syncthreads().
 __device__ __forceinline__ void team_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -210,6 +223,13 @@ __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); 
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Packed fp32x2 arithmetic (one issue slot for two lanes on sm_100).
+#ifdef IXB_SCALAR_PAIRS
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+#else
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;"
@@ -235,5 +255,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
         "l"(*reinterpret_cast<const unsigned long long*>(&b)));
   return d;
 }
+#endif
 
 }  // namespace ixb

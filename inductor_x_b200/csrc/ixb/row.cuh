@@ -15,12 +15,15 @@
 //   struct Params         plain-old-data kernel argument
 //   kRowInputs            number of row-shaped inputs prefetched by the template
 //   row_ptr(p, k)         base pointer of row input k
-//   init(p, ctx)          once per thread (cache per-column constants)
+//   smem_bytes(cols, vpt) CTA-shared scratch the body wants (0 for most)
+//   init(p, ctx, smem)    once per thread (cache per-column constants); ends with a
+//                         CTA-wide barrier if it filled the scratch
 //   row(p, ctx, r, raw)   process row r given its raw vectors raw[k][i]
 #pragma once
 #include <type_traits>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ixb {
 
@@ -87,6 +90,55 @@ template <typename T, int TEAM, int TEAMS, int VPT, bool ALIGNED> struct RowCtx 
     }
     return v;
   }
+  // Online-softmax reduction: one exchange for a maximum, NS sums that were accumulated
+  // relative to each thread's own maximum, and NP ordinary sums (NS + NP <= 3).
+  // In: m = this thread's maximum; scaled[n] = sum of terms exp2((x - m) * k);
+  // plain[n] = any partial sum.  Out: m = team maximum, scaled[n] = team totals relative
+  // to it, plain[n] = team totals.  Returns this thread's factor
+  // exp2((m_thread - m_team) * k), by which its own terms must be scaled.
+  template <int NS, int NP>
+  __device__ __forceinline__ float reduce_rescaled(float& m, float (&scaled)[NS],
+                                                   float (&plain)[NP > 0 ? NP : 1], float k) {
+    static_assert(NS + NP <= 3, "exchange slot holds a maximum and three sums");
+    const float mt = m;
+    const float mw = warp_max_fast(mt);
+    float r = (mt == -INFINITY) ? 0.f : fast_exp2((mt - mw) * k);
+    float v[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < NS; ++n) v[n] = warp_reduce<SumOp>(scaled[n] * r);
+#pragma unroll
+    for (int n = 0; n < NP; ++n) v[NS + n] = warp_reduce<SumOp>(plain[n]);
+    if constexpr (TEAM > 32) {
+      float* slot = red + phase * kWarpsPerTeam * 4;
+      if ((lane & 31) == 0)
+        *reinterpret_cast<float4*>(slot + (lane >> 5) * 4) = make_float4(mw, v[0], v[1], v[2]);
+      team_barrier(team + 1, TEAM);
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarpsPerTeam; ++w) mm = fmaxf(mm, slot[w * 4]);
+      v[0] = v[1] = v[2] = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarpsPerTeam; ++w) {
+        const float4 part = *reinterpret_cast<const float4*>(slot + w * 4);
+        const float f = (part.x == -INFINITY) ? 0.f : fast_exp2((part.x - mm) * k);
+        const float pv[3] = {part.y, part.z, part.w};
+#pragma unroll
+        for (int n = 0; n < NS; ++n) v[n] = fmaf(pv[n], f, v[n]);
+#pragma unroll
+        for (int n = 0; n < NP; ++n) v[NS + n] += pv[NS + n];
+      }
+      r *= (mw == -INFINITY) ? 0.f : fast_exp2((mw - mm) * k);
+      m = mm;
+      phase ^= 1;
+    } else {
+      m = mw;
+    }
+#pragma unroll
+    for (int n = 0; n < NS; ++n) scaled[n] = v[n];
+#pragma unroll
+    for (int n = 0; n < NP; ++n) plain[n] = v[NS + n];
+    return r;
+  }
   // Two sums at once (one barrier instead of two).
   __device__ __forceinline__ float2 reduce_sum2(float a, float b) {
     a = warp_reduce<SumOp>(a);
@@ -129,14 +181,15 @@ template <typename T, int TEAM, int TEAMS, int VPT, bool ALIGNED> struct RowCtx 
   }
 };
 
-template <class Body, int TEAM, int TEAMS, int VPT, bool ALIGNED>
-__global__ void __launch_bounds__(TEAM* TEAMS)
+template <class Body, int TEAM, int TEAMS, int VPT, bool ALIGNED, int MIN_CTAS = 1>
+__global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
     row_kernel(const typename Body::Params p, const long long rows, const int cols) {
   using T = typename Body::in_t;
   using Ctx = RowCtx<T, TEAM, TEAMS, VPT, ALIGNED>;
   constexpr int NIN = Body::kRowInputs;
   // [team][phase][warp] with 4 floats per warp so arg-reductions fit as well
   __shared__ __align__(16) float exchange[TEAMS * 2 * (TEAM / 32) * 4];
+  extern __shared__ __align__(128) unsigned char body_smem[];  // Body::smem_bytes(cols, VPT)
 
   Ctx c;
   c.lane = threadIdx.x % TEAM;
@@ -146,7 +199,7 @@ __global__ void __launch_bounds__(TEAM* TEAMS)
   c.red = exchange + c.team * 2 * (TEAM / 32) * 4;
 
   typename Body::template Impl<VPT> body;
-  body.init(p, c);
+  body.init(p, c, body_smem);
 
   const long long stride = (long long)gridDim.x * TEAMS;
   long long r = (long long)blockIdx.x * TEAMS + c.team;
@@ -174,24 +227,156 @@ __global__ void __launch_bounds__(TEAM* TEAMS)
   }
 }
 
-// Host launcher: persistent grid = min(row groups, SMs x resident CTAs).
-template <class Body, int TEAM, int TEAMS, int VPT, bool ALIGNED>
-cudaError_t launch_row(const typename Body::Params& p, long long rows, int cols, int sm_count,
-                       int grid_override, cudaStream_t stream) {
-  auto kern = row_kernel<Body, TEAM, TEAMS, VPT, ALIGNED>;
-  static int resident = 0;  // CTAs per SM; identical on every B200 of a box
+// Staged variant: rows arrive in a shared-memory ring filled by bulk asynchronous copies
+// (one TMA instruction per row, issued by lane 0 of the team) STAGES-1 rows ahead, so the
+// bytes in flight per SM no longer depend on how many registers a thread can spare for
+// prefetch.  Needs ALIGNED rows: 16-byte aligned base and a row pitch that is a multiple
+// of 16 bytes.  Ring layout: [team][stage][input][row bytes].
+template <class Body, int TEAM, int TEAMS, int VPT, int STAGES, int MIN_CTAS>
+__global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
+    row_staged_kernel(const typename Body::Params p, const long long rows, const int cols) {
+  using T = typename Body::in_t;
+  using Ctx = RowCtx<T, TEAM, TEAMS, VPT, true>;
+  constexpr int NIN = Body::kRowInputs;
+  extern __shared__ __align__(128) unsigned char ring_raw[];
+  __shared__ __align__(16) float exchange[TEAMS * 2 * (TEAM / 32) * 4];
+  __shared__ __align__(8) uint64_t full[TEAMS][STAGES];
+
+  Ctx c;
+  c.lane = threadIdx.x % TEAM;
+  c.team = threadIdx.x / TEAM;
+  c.cols = cols;
+  c.phase = 0;
+  c.red = exchange + c.team * 2 * (TEAM / 32) * 4;
+
+  const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
+  // body scratch first (rounded up to 128 bytes), then the rings
+  const size_t body_bytes = (Body::smem_bytes(cols, VPT) + 127) & ~(size_t)127;
+  unsigned char* ring = ring_raw + body_bytes + (size_t)c.team * STAGES * NIN * row_bytes;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int t = 0; t < TEAMS; ++t)
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) mbar_init(&full[t][s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  typename Body::template Impl<VPT> body;
+  body.init(p, c, ring_raw);
+
+  const long long stride = (long long)gridDim.x * TEAMS;
+  const long long r0 = (long long)blockIdx.x * TEAMS + c.team;
+
+  auto issue = [&](long long row, int slot) {
+    mbar_arrive_expect_tx(&full[c.team][slot], row_bytes * NIN);
+#pragma unroll
+    for (int k = 0; k < NIN; ++k)
+      bulk_g2s(ring + ((size_t)slot * NIN + k) * row_bytes,
+               Body::row_ptr(p, k) + row * (long long)cols, row_bytes, &full[c.team][slot]);
+  };
+  if (c.lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      const long long row = r0 + (long long)s * stride;
+      if (row < rows) issue(row, s);
+    }
+  }
+
+  int slot = 0;
+  uint32_t parity = 0;
+  bool ok = true;
+  for (long long r = r0; r < rows; r += stride) {
+    if (!mbar_wait(&full[c.team][slot], parity)) {
+      ok = false;
+      break;
+    }
+    uint4 cur[NIN][VPT];
+#pragma unroll
+    for (int k = 0; k < NIN; ++k) {
+      const unsigned char* src = ring + ((size_t)slot * NIN + k) * row_bytes;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+        cur[k][i] = c.valid(i) ? *reinterpret_cast<const uint4*>(src + (size_t)c.vec_col(i) * sizeof(T))
+                               : make_uint4(0, 0, 0, 0);
+    }
+    // every thread of the team has taken its vectors: the slot can be refilled
+    if constexpr (TEAM > 32) team_barrier(c.team + 1, TEAM); else __syncwarp();
+    if (c.lane == 0) {
+      const long long nr = r + (long long)STAGES * stride;
+      if (nr < rows) issue(nr, slot);
+    }
+    body.row(p, c, r, cur);
+    if (++slot == STAGES) {
+      slot = 0;
+      parity ^= 1;
+    }
+  }
+  if (!ok) {
+    // a wait gave up: drain what this team still has in flight (bounded) before the CTA's
+    // shared memory is released, then leave
+    for (int s = 0; s < STAGES; ++s) mbar_wait(&full[c.team][s], parity);
+  }
+}
+
+template <class Body, int TEAM, int TEAMS, int VPT, int STAGES, int MIN_CTAS>
+cudaError_t launch_row_staged(const typename Body::Params& p, long long rows, int cols,
+                              int sm_count, int grid_override, cudaStream_t stream) {
+  auto kern = row_staged_kernel<Body, TEAM, TEAMS, VPT, STAGES, MIN_CTAS>;
+  const size_t smem = ((Body::smem_bytes(cols, VPT) + 127) & ~(size_t)127) +
+                      (size_t)TEAMS * STAGES * Body::kRowInputs * cols * sizeof(typename Body::in_t);
+  static int resident = 0;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+    resident = 0;
+  }
   if (resident == 0) {
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, 0);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, smem);
     if (e != cudaSuccess) return e;
-    resident = n > 0 ? n : 1;
+    if (n < 1) return cudaErrorInvalidConfiguration;
+    resident = n;
   }
   const long long groups = (rows + TEAMS - 1) / TEAMS;
   long long grid = (long long)sm_count * resident;
   if (grid_override > 0) grid = grid_override;
   if (grid > groups) grid = groups;
   if (grid < 1) return cudaSuccess;
-  kern<<<(unsigned)grid, TEAM * TEAMS, 0, stream>>>(p, rows, cols);
+  kern<<<(unsigned)grid, TEAM * TEAMS, smem, stream>>>(p, rows, cols);
+  return cudaGetLastError();
+}
+
+// Host launcher: persistent grid = min(row groups, SMs x resident CTAs).
+template <class Body, int TEAM, int TEAMS, int VPT, bool ALIGNED, int MIN_CTAS = 1>
+cudaError_t launch_row(const typename Body::Params& p, long long rows, int cols, int sm_count,
+                       int grid_override, cudaStream_t stream) {
+  auto kern = row_kernel<Body, TEAM, TEAMS, VPT, ALIGNED, MIN_CTAS>;
+  const size_t smem = Body::smem_bytes(cols, VPT);
+  static int resident = 0;  // CTAs per SM; identical on every B200 of a box
+  static size_t configured = 0, sized_for = (size_t)-1;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  if (resident == 0 || sized_for != smem) {
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, smem);
+    if (e != cudaSuccess) return e;
+    if (n < 1) return cudaErrorInvalidConfiguration;
+    resident = n;
+    sized_for = smem;
+  }
+  const long long groups = (rows + TEAMS - 1) / TEAMS;
+  long long grid = (long long)sm_count * resident;
+  if (grid_override > 0) grid = grid_override;
+  if (grid > groups) grid = groups;
+  if (grid < 1) return cudaSuccess;
+  kern<<<(unsigned)grid, TEAM * TEAMS, smem, stream>>>(p, rows, cols);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,65 @@
+// mbarrier and bulk-copy (TMA) primitives with bounded waits.  Every spin has an
+// iteration limit; a wait that runs out bumps a device-side counter the host can read
+// (ixb_pipeline_timeouts) and the caller leaves its loop instead of hanging the SM.
+#pragma once
+#include "common.cuh"
+
+namespace ixb {
+
+// Number of mbarrier waits that gave up since the library was loaded on this device.
+// One copy per translation unit (the library is built without relocatable device code);
+// each unit that includes this header exposes its copy through IXB_DEFINE_TIMEOUT_READER.
+static __device__ unsigned int g_wait_timeouts = 0;
+#define IXB_DEFINE_TIMEOUT_READER(fn_name)                                              \
+  cudaError_t fn_name(unsigned int* out) {                                              \
+    return cudaMemcpyFromSymbol(out, ixb::g_wait_timeouts, sizeof(unsigned int));       \
+  }
+
+constexpr uint32_t kSpinLimit = 1u << 22;  // try_wait attempts (each suspends up to ~ms)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false = gave up (counter bumped once per failing thread).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicAdd(&g_wait_timeouts, 1u);
+  return false;
+}
+// Bulk asynchronous copy global -> shared, completion counted in bytes on `bar`.
+// Both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                         uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+}  // namespace ixb
