@@ -166,6 +166,30 @@ int ixb_outer_reduce(int dtype, int kind, const void* x, void* out, int64_t oute
                      int64_t inner, void* scratch, size_t scratch_bytes, const ixb_cfg* cfg,
                      ixb_stream stream);
 
+/* Capacity of the built-in scratch used by ixb_outer_reduce_static. */
+#define IXB_STATIC_SCRATCH_BYTES (4u * 1024u * 1024u)
+
+/* No counterpart in the reference: an addition for callers that cannot allocate.
+ * Same result as ixb_outer_reduce with cfg->rsplit = rsplit, but the fp32 partials of
+ * the split go to a fixed IXB_STATIC_SCRATCH_BYTES array that is part of the library
+ * image (each GPU that loads the library holds those 4 MiB until the process exits), so
+ * neither the caller nor the library allocates anything.  It is meant for code that runs
+ * where a device allocation is off the table: a wrapper whose buffers were all planned
+ * and reserved ahead of time, a serving loop in which cudaMalloc would stall every
+ * stream of the device, or a process whose GPU memory is already owned by a caching
+ * allocator so that a raw allocation may simply fail.
+ *   - outer * inner * rsplit * 4 must not exceed IXB_STATIC_SCRATCH_BYTES, otherwise
+ *     IXB_ERR_SCRATCH is returned and nothing is launched; x must be 16-byte aligned
+ *     and inner a multiple of 16 bytes (IXB_ERR_ALIGN otherwise); rsplit >= 1.
+ *   - The first call on each device looks up the array's device address (with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  Every launch overwrites the partials
+ *     it later reads, so nothing needs clearing between calls, but two calls whose
+ *     kernels overlap on the GPU (different streams, no ordering) race on it: keep
+ *     calls on one stream or order them with events. */
+int ixb_outer_reduce_static(int dtype, int kind, const void* x, void* out, int64_t outer,
+                            int64_t R, int64_t inner, int rsplit, ixb_stream stream);
+
 /* ---- SHORT_ROW family ------------------------------------------------------------- */
 
 /* x contiguous [A,B,C,L]; the stride-1 axis L (L*elsize a power-of-two multiple of 16 up

@@ -96,6 +96,8 @@ _SIGNATURES = {
     "ixb_outer_reduce_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int]),
     "ixb_outer_reduce": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                  c_size_t, POINTER(IxbCfg), c_void_p]),
+    "ixb_outer_reduce_static": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                        c_void_p]),
     "ixb_short_row_reduce": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                      c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "ixb_index_select_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
