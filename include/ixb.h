@@ -213,6 +213,25 @@ int ixb_index_select_rows(const void* table, const void* idx, void* out, int64_t
                           int64_t m, int64_t row_bytes, int64_t table_pitch_bytes, int idx_dtype,
                           int wrap_negative, int32_t* status, ixb_stream stream);
 
+/* ---- fused attention ----------------------------------------------------------------- */
+
+/* out = softmax(q k^T * scale [+ causal mask]) v for q[B,H,Sq,D], k/v[B,H,Sk,D], D = 128,
+ * dtype F16 or BF16, fp32 accumulation; lse[B,H,Sq] (fp32, natural log of the softmax
+ * denominator times exp of the row maximum, i.e. logsumexp of the scaled scores) may be
+ * NULL.  *_strides = element strides of the (batch, head, sequence) axes; the D axis must
+ * be contiguous and every stride a multiple of 8 elements, so both the reference's BNSD
+ * layout and a transposed BSND view are taken without a copy.  causal != 0 masks key j
+ * for query i when j > i + (Sk - Sq) and requires Sk >= Sq.  `status` is NULL or a device
+ * word zeroed by the caller; it is set to 1 if an internal wait gave up (results are then
+ * undefined).  Stands in for the vendor call torch_npu.npu_fusion_attention behind
+ * npu_graph::npu_fa (inductor_x/npu_fusion_attention_graph.py:20-35); note that entry
+ * takes the softmax multiplier itself, whereas the reference passes inv_scale and inverts
+ * it inside the op (inductor_x/npu_fusion_attention_graph.py:22-29,162). */
+int ixb_fa_fwd(int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
+               int32_t B, int32_t H, int32_t Sq, int32_t Sk, int32_t D, const int64_t* q_strides,
+               const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+               float scale, int causal, int32_t* status, ixb_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

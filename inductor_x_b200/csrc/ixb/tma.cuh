@@ -15,7 +15,7 @@ static __device__ unsigned int g_wait_timeouts = 0;
     return cudaMemcpyFromSymbol(out, ixb::g_wait_timeouts, sizeof(unsigned int));       \
   }
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // try_wait attempts (each suspends up to ~ms)
+constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -45,12 +45,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait; false = gave up (counter bumped once per failing thread).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+// Bounded wait: gives up after about a second of SM clock (counter bumped), or as soon as
+// `abort` (a flag another role of the CTA raises when its own wait gave up) is non-zero.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          const volatile int* abort = nullptr) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-  atomicAdd(&g_wait_timeouts, 1u);
-  return false;
+    if (abort != nullptr && *abort != 0) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicAdd(&g_wait_timeouts, 1u);
+      return false;
+    }
+  }
 }
 // Bulk asynchronous copy global -> shared, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, `bytes` a multiple of 16.

@@ -183,3 +183,38 @@ def index_select_rows(table: torch.Tensor, idx: torch.Tensor, *, wrap_negative: 
         if flag:
             raise IndexError(f"index_select_rows: index out of range at position {pos}")
     return out
+
+
+def _bhs_strides(t: torch.Tensor):
+    arr = (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    return arr
+
+
+def fused_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, *,
+                    causal: bool = False, return_lse: bool = False, check: bool = False):
+    """``softmax(q @ k^T * scale [+ causal mask]) @ v`` for ``[B, H, S, D]`` tensors
+    (any batch/head/sequence strides, ``D`` contiguous, ``D == 128``, fp16 or bf16).
+
+    Returns ``out`` (contiguous ``[B, H, Sq, D]``) or ``(out, lse)`` with ``lse`` the fp32
+    log-sum-exp of the scaled scores ``[B, H, Sq]``.  ``check=True`` reads the kernel's
+    status word back (synchronises) and raises if an internal wait gave up."""
+    _need_cuda(q, k, v)
+    if q.dim() != 4 or k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
+        raise ValueError("expected q[B,H,Sq,D], k[B,H,Sk,D], v[B,H,Sk,D]")
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k, v must share dtype float16 or bfloat16")
+    for t in (q, k, v):
+        if t.stride(3) != 1:
+            raise ValueError("the head dimension must be contiguous")
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    out = torch.empty((B, H, Sq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
+    rt.check("ixb_fa_fwd", rt.load().ixb_fa_fwd(
+        rt.DTYPE_CODE[q.dtype], q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), rt.ptr(lse),
+        B, H, Sq, Sk, D, _bhs_strides(q), _bhs_strides(k), _bhs_strides(v), _bhs_strides(out),
+        float(scale), int(causal), rt.ptr(status), rt.raw_stream(q.device)))
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError("ixb_fa_fwd: an internal pipeline wait gave up; output is undefined")
+    return (out, lse) if return_lse else out

@@ -100,6 +100,9 @@ _SIGNATURES = {
                                         c_void_p]),
     "ixb_short_row_reduce": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                      c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "ixb_fa_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                           c_int32, c_int32, c_int32, POINTER(c_int64), POINTER(c_int64),
+                           POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_void_p, c_void_p]),
     "ixb_index_select_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                       c_int, c_int, c_void_p, c_void_p]),
 }

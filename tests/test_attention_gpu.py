@@ -1,0 +1,118 @@
+"""GPU parity tests of the fused-attention kernel (tcgen05 / TMEM / TMA) through the C ABI.
+
+Tolerance: 2e-2 relative to max(|expected|, rms(expected)) for fp16 / bf16 outputs;
+log-sum-exp within 2e-3 absolute (it is accumulated in fp32)."""
+import math
+
+import pytest
+import torch
+
+from inductor_x_b200 import ops
+from inductor_x_b200 import runtime as rt
+from oracle import c_oracle, graphs, inputs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def run(d, cuda, causal, **kw):
+    q, k, v = (d[n].to(cuda) for n in "qkv")
+    return ops.fused_attention(q, k, v, d["scale"], causal=causal, return_lse=True, check=True, **kw)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 384), (1, 1, 1000), (1, 2, 77),
+                                   (2, 2, 1536)])
+def test_attention_vs_oracle(cuda, dtype, causal, B, H, S):
+    d = inputs.c4(B, H, S, 128, seed=B * 100 + S, dtype=dtype)
+    out, lse = run(d, cuda, causal)
+    exp, else = graphs.attention(d["q"], d["k"], d["v"], d["scale"], causal=causal)
+    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+    assert float((lse.cpu() - else).abs().max()) <= 2e-3
+
+
+def test_attention_vs_c_oracle_small(cuda):
+    d = inputs.c4(1, 2, 160, 128, seed=9)
+    out, lse = run(d, cuda, True)
+    exp, else = c_oracle.attention(d["q"], d["k"], d["v"], d["scale"], causal=True)
+    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+    assert float((lse.cpu().double() - else).abs().max()) <= 2e-3
+
+
+def test_attention_cross_lengths(cuda):
+    # Sk > Sq: non-causal and bottom-right aligned causal
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(1, 2, 130, 128, generator=g).bfloat16()
+    k = torch.randn(1, 2, 450, 128, generator=g).bfloat16()
+    v = torch.randn(1, 2, 450, 128, generator=g).bfloat16()
+    sc = 1 / math.sqrt(128)
+    for causal in (False, True):
+        out = ops.fused_attention(q.to(cuda), k.to(cuda), v.to(cuda), sc, causal=causal, check=True)
+        exp, _ = graphs.attention(q, k, v, sc, causal=causal)
+        assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+
+
+def test_attention_transposed_layout_no_copy(cuda):
+    # [B, S, N, D] storage viewed as [B, N, S, D], as the reference's replacement produces
+    # with query.transpose(1, 2) (inductor_x/npu_fusion_attention_graph.py:150-164)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, 300, 4, 128, generator=g).bfloat16() for _ in range(3))
+    qd, kd, vd = (t.to(cuda).transpose(1, 2) for t in (q, k, v))
+    assert not qd.is_contiguous()
+    out = ops.fused_attention(qd, kd, vd, 0.1, causal=False, check=True)
+    exp = graphs.attention_pattern(q.float(), k.float(), v.float(), 10.0)
+    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+
+
+def test_attention_reference_pattern_golden(cuda, golden):
+    # the reference's own search pattern (fp32 eager) on its [B, S, N, D] inputs
+    p = inputs.c4_pattern(2, 96, 3, 128, seed=4)
+    exp = graphs.attention_pattern(p["query"], p["key"], p["value"], p["inv_scale_factor"])
+    q, k, v = (p[n].bfloat16().to(cuda).transpose(1, 2) for n in ("query", "key", "value"))
+    out = ops.fused_attention(q, k, v, 1.0 / p["inv_scale_factor"], causal=False, check=True)
+    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+
+
+def test_attention_large_scores_rescale_path(cuda):
+    # scores that keep growing along the key axis force the lazy O rescale to trigger
+    B, H, S = 1, 1, 1024
+    q = torch.ones(B, H, S, 128)
+    k = (torch.arange(S).float() / S * 3).view(1, 1, S, 1).expand(B, H, S, 128).contiguous()
+    v = torch.randn(B, H, S, 128, generator=torch.Generator().manual_seed(1))
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out, lse = ops.fused_attention(q.to(cuda), k.to(cuda), v.to(cuda), 1.0, causal=False,
+                                   return_lse=True, check=True)
+    exp, else = graphs.attention(q, k, v, 1.0, causal=False)
+    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+    assert float((lse.cpu() - else).abs().max()) <= 5e-3 * float(else.abs().max())
+
+
+def test_attention_full_size_rows_vs_golden(cuda, golden):
+    d = inputs.c4()
+    out, lse = run(d, cuda, True)
+    rows = golden["c4_rows"].tolist()
+    for i, (b, h) in enumerate(golden["c4_heads"].tolist()):
+        got = out[b, h][rows].cpu()
+        assert graphs.max_rel_err(got, golden["c4_out_rows"][i]) <= TOL
+        assert float((lse[b, h][rows].cpu() - golden["c4_lse_rows"][i]).abs().max()) <= 2e-3
+    # size-independent property: causal row 0 attends to key 0 only -> out[0] == v[0]
+    assert torch.equal(out[:, :, 0].cpu(), d["v"][:, :, 0])
+    # and every output row is a convex combination of V rows
+    assert float(out.float().abs().max()) <= float(d["v"].float().abs().max()) + 1e-3
+
+
+def test_attention_argument_errors(cuda):
+    q = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(rt.IxbError) as e:
+        ops.fused_attention(q, q, q, 1.0)
+    assert e.value.status == rt.IXB_ERR_SHAPE  # head dim != 128
+    q = torch.zeros(1, 1, 8, 128, dtype=torch.float32, device=cuda)
+    with pytest.raises(ValueError):
+        ops.fused_attention(q, q, q, 1.0)
+    q = torch.zeros(1, 1, 300, 128, dtype=torch.bfloat16, device=cuda)
+    k = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(rt.IxbError):
+        ops.fused_attention(q, k, k, 1.0, causal=True)  # causal with Sk < Sq
+    empty = ops.fused_attention(q[:, :, :0], k, k, 1.0)
+    assert empty.shape == (1, 1, 0, 128)
