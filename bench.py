@@ -341,9 +341,66 @@ class IndexSelect:
         return fn, self.algorithmic_bytes(), "full workload, torch.index_select on CPU"
 
 
+class FusedAttention:
+    """configs[3]: causal attention, B=8, H=32, S=4096, D=128, bf16 (batch sharded over GPUs)."""
+
+    name = "fused_attention_bf16_b8_h32_s4096_d128_causal"
+    dtype = "bf16"
+    B, H, S, D = 8, 32, 4096, 128
+    metric = "fused-attention TFLOP/s"
+    unit = "TFLOP/s"
+    bound = "tensor"
+
+    def flops(self):
+        # causal-half convention: 4 * B * H * S^2 * D / 2
+        return 4 * self.B * self.H * self.S * self.S * self.D // 2
+
+    def algorithmic_bytes(self):
+        return 4 * self.B * self.H * self.S * self.D * 2
+
+    def load_host(self, seed):
+        from oracle import inputs
+
+        self.host = inputs.c4(self.B, self.H, self.S, self.D, seed=seed)
+        return self.host
+
+    def setup(self, device, seed, n_sets=1):
+        d = self.load_host(seed)
+        self.q, self.k, self.v = (d[n].to(device) for n in "qkv")
+        self.scale = d["scale"]
+        self.xs = [self.q]
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        self.out = ops.fused_attention(self.q, self.k, self.v, self.scale, causal=True)
+        return 1
+
+    def e2e_setup(self, device):
+        self.h = [self.host[n].pin_memory() for n in "qkv"]
+        self.d = [torch.empty_like(self.q) for _ in range(3)]
+        self.h_o = torch.empty_like(self.h[0]).pin_memory()
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        for dst, src in zip(self.d, self.h):
+            dst.copy_(src, non_blocking=True)
+        o = ops.fused_attention(self.d[0], self.d[1], self.d[2], self.scale, causal=True)
+        self.h_o.copy_(o, non_blocking=True)
+        return 3 * self.h[0].numel() * 2, self.h_o.numel() * 2
+
+    def cpu_sample(self, heads=2):
+        import torch.nn.functional as F
+
+        q, k, v = (self.host[n][:1, :heads].float() for n in "qkv")
+        fn = lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=self.scale)
+        return fn, 4 * heads * self.S * self.S * self.D // 2, f"{heads} of {self.B * self.H} heads, CPU SDPA fp32"
+
+
 WORKLOADS = {
     "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
-    "c3a_sum": PermutedSum, "c3b": IndexSelect,
+    "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention,
 }
 
 
@@ -463,7 +520,9 @@ def main():
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     nbytes = wl.algorithmic_bytes()
-    value = world * nbytes / (ms_per_step * 1e-3) / 1e9
+    tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
+    work = wl.flops() / 1e3 if tensor_bound else nbytes  # per step; /1e3 so that /1e9 gives tera
+    value = world * work / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the public op with host buffers
     wl.e2e_setup(device)
@@ -482,7 +541,7 @@ def main():
         t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_value = world * nbytes / (e2e_ms / args.e2e_steps * 1e-3) / 1e9
+    e2e_value = world * work / (e2e_ms / args.e2e_steps * 1e-3) / 1e9
 
     if rank == 0:
         sampler.stop_flag.set()
@@ -494,31 +553,34 @@ def main():
             torch.set_num_threads(os.cpu_count() or 1)
             fn, cbytes, sample = wl.cpu_sample()
             best = time_cpu(fn)
-            cpu = {"value": cbytes / best / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+            cpu = {"value": cbytes / best / (1e12 if tensor_bound else 1e9),
+                   "unit": "TFLOP/s" if tensor_bound else "GB/s", "cores": torch.get_num_threads(),
                    "kind": "port", "sample": sample + f"; best of >=5, {best * 1e3:.2f} ms"}
 
-        achieved = nbytes / (avg_kernel_ms * 1e-3) / 1e9
+        achieved = work / (avg_kernel_ms * 1e-3) / 1e9
+        peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
+        unit = "TFLOP/s" if tensor_bound else "GB/s"
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tpath):
             with open(tpath) as f:
                 traffic = json.load(f).get(wl.name)
         line = {
-            "metric": "fused-kernel HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "metric": getattr(wl, "metric", "fused-kernel HBM GB/s"), "value": value, "unit": unit,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic",
             "config": {"workload": wl.name, "algorithmic_bytes_per_step": nbytes,
                        "l2": "working set per step exceeds the 126 MB L2 and steps rotate over "
                              f"{len(getattr(wl, 'xs', getattr(wl, 'idxs', [0])))} distinct buffer sets",
                        "sharding": f"rows split over {world} GPU(s), no collective"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+            "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
+                         "unit": unit, "frac": achieved / peak, "traffic": traffic,
                          "peak_source": peaks["source"], "kernel_ms_avg": avg_kernel_ms,
                          "kernel_ms_median": kernel_ms[len(kernel_ms) // 2],
-                         "frac_of_nominal_8TBs": achieved / 8000.0},
+                         "frac_of_nominal": achieved / (2250.0 if tensor_bound else 8000.0)},
             "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.e2e_steps},
             "gpu_launches": launches,
             "clocks": clocks,

@@ -3,20 +3,22 @@
 // It takes the place of the vendor kernel behind torch.ops.npu_graph.npu_fa
 // (inductor_x/npu_fusion_attention_graph.py:20-35).
 //
-// One CTA owns a 128-row query tile of one (batch, head) and walks the key/value tiles
-// (128 keys each) that the tile can see.  Six warps, three roles:
+// One CTA owns two 128-row query tiles (A, B) of one (batch, head) and walks the
+// key/value tiles (128 keys each) that they can see.  Ten warps, three roles:
 //   warp 0     TMA producer: Q once, then K_j / V_j into two-stage rings
-//   warp 1     MMA issuer: S_j = Q K_j^T into one of two TMEM buffers, then O += P_j V_j
-//              with P_j read straight from TMEM (it overwrites S_j as 16-bit values)
-//   warps 2-5  softmax: thread <-> query row.  Reads its S row from TMEM, applies scale
-//              and mask, keeps a running maximum and sum, writes P_j back to TMEM, and
-//              rescales the O accumulator only when the maximum has grown by more than
-//              2^8 since the last rescale (the final division by the sum makes any stale
-//              reference maximum exact).
+//   warp 1     MMA issuer: S_t(j) = Q_t K_j^T into tile t's TMEM buffer, then
+//              O_t += P_t(j) V_j with P read straight from TMEM (it overwrites S as 16-bit
+//              values).  The two tiles alternate, so the tensor core works on one tile
+//              while the other tile's softmax runs.
+//   warps 2-5  softmax of tile A, warps 6-9 softmax of tile B: thread <-> query row.
+//              Pass 1 reads the S row for its maximum; pass 2 re-reads it 32 columns at
+//              a time, exponentiates and writes P back.  The O accumulator is rescaled
+//              only when the maximum has grown by more than 2^8 since the last rescale
+//              (the final division by the running sum makes a stale reference exact).
 // Hand-offs are mbarriers; every wait is bounded and a wait that gives up raises a flag in
 // `status` and lets the CTA drain and exit.
 //
-// TMEM columns: [0,128) S/P buffer 0, [128,256) S/P buffer 1, [256,384) O.
+// TMEM columns: [0,128) S/P of A, [128,256) S/P of B, [256,384) O of A, [384,512) O of B.
 #include "host.h"
 #include "ixb/tcgen05.cuh"
 
@@ -24,17 +26,18 @@ namespace {
 
 using namespace ixb;
 
-constexpr int BM = 128;          // query rows per CTA
+constexpr int BM = 128;          // rows of one query tile
+constexpr int NQ = 2;            // query tiles per CTA
 constexpr int BN = 128;          // keys per tile
 constexpr int HD = 128;          // head dimension
 constexpr int kStages = 2;
-constexpr int kTileBytes = BN * HD * 2;   // one operand tile, 16-bit elements
+constexpr int kTileBytes = BN * HD * 2;     // one operand tile, 16-bit elements
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column TMA box of the tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 64 + NQ * 128;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
-constexpr float kRescaleThreshold = 8.f;  // log2 units
-constexpr size_t kSmemBytes = (size_t)kTileBytes * (1 + 2 * kStages) + 1024;
+constexpr uint32_t kColS = 0, kColO = 256;  // + 128 * tile
+constexpr float kRescaleThreshold = 8.f;    // log2 units
+constexpr size_t kSmemBytes = (size_t)kTileBytes * (NQ + 2 * kStages) + 1024;
 
 struct FaParams {
   void* o;
@@ -42,7 +45,7 @@ struct FaParams {
   int* status;           // device word set to 1 if a wait gave up, may be null
   long long o_stride_b, o_stride_h, o_stride_s;  // elements
   int B, H, Sq, Sk;
-  float scale_log2;      // softmax scale * log2(e)
+  float scale_log2;      // softmax scale * log2(e), > 0
   int causal;
 };
 
@@ -64,11 +67,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_smem = smem;
-  unsigned char* k_smem = smem + kTileBytes;
-  unsigned char* v_smem = smem + kTileBytes * (1 + kStages);
+  unsigned char* k_smem = smem + kTileBytes * NQ;
+  unsigned char* v_smem = smem + kTileBytes * (NQ + kStages);
 
   __shared__ __align__(8) uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages],
-      v_empty[kStages], s_full[2], p_full[2], pv_done[2];
+      v_empty[kStages], s_full[NQ], p_full[NQ], pv_done[NQ];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int failed;
 
@@ -76,18 +79,26 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
 
   // heavy (late) query tiles first: they see the most keys under a causal mask
-  const int n_q_tiles = (p.Sq + BM - 1) / BM;
-  const int q_tile = n_q_tiles - 1 - (int)blockIdx.x;
+  const int n_q_blocks = (p.Sq + BM * NQ - 1) / (BM * NQ);
+  const int q_block = n_q_blocks - 1 - (int)blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
-  const int q0 = q_tile * BM;
-  const int diag = p.Sk - p.Sq;  // key index allowed for query row i: j <= i + diag
-  int kv_end = p.Sk;
-  if (p.causal) {
-    const int lim = q0 + BM + diag;
-    kv_end = lim < p.Sk ? lim : p.Sk;
+  const int q0 = q_block * BM * NQ;
+  const int diag = p.Sk - p.Sq;  // key j is visible to query row i when j <= i + diag
+  // number of key tiles each query tile walks (0 for a tile past the end of the sequence)
+  int n_kv_t[NQ];
+  int n_kv = 0;
+#pragma unroll
+  for (int t = 0; t < NQ; ++t) {
+    const int qt0 = q0 + t * BM;
+    int kv_end = p.Sk;
+    if (p.causal) {
+      const int lim = qt0 + BM + diag;
+      kv_end = lim < p.Sk ? lim : p.Sk;
+    }
+    n_kv_t[t] = qt0 < p.Sq ? (kv_end + BN - 1) / BN : 0;
+    n_kv = n_kv_t[t] > n_kv ? n_kv_t[t] : n_kv;
   }
-  const int n_kv = (kv_end + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -97,10 +108,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
-      mbar_init(&pv_done[s], 1);
+    for (int t = 0; t < NQ; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&pv_done[t], 1);
     }
     failed = 0;
     mbar_init_fence();
@@ -115,9 +126,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
-      mbar_arrive_expect_tx(&q_full, kTileBytes);
-      tc::tma_load_4d(q_smem, &map_q, &q_full, 0, q0, h, b);
-      tc::tma_load_4d(q_smem + kHalfBytes, &map_q, &q_full, 64, q0, h, b);
+      mbar_arrive_expect_tx(&q_full, kTileBytes * NQ);
+#pragma unroll
+      for (int t = 0; t < NQ; ++t) {
+        // rows past the end of the tensor are zero-filled by the copy engine
+        tc::tma_load_4d(q_smem + t * kTileBytes, &map_q, &q_full, 0, q0 + t * BM, h, b);
+        tc::tma_load_4d(q_smem + t * kTileBytes + kHalfBytes, &map_q, &q_full, 64, q0 + t * BM, h, b);
+      }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j % kStages, n = j / kStages;
         if (n > 0) ok = mbar_wait(&k_empty[s], (n - 1) & 1, &failed);
@@ -141,12 +156,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::instr_desc(BM, BN, IS_BF16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = tc::instr_desc(BM, HD, IS_BF16 ? 1 : 0, 0, 1);
-      const uint32_t q_addr = smem_u32(q_smem);
-      // S_j = Q K_j^T: both operands K-major, 8 steps of 16 along the head dimension;
+      // S_t = Q_t K_j^T: both operands K-major, 8 steps of 16 along the head dimension;
       // a step moves 32 bytes inside the 128-byte swizzled row, 4 steps per 64-column box
-      auto issue_qk = [&](int buf, int stage) {
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t q_addr = smem_u32(q_smem + (size_t)t * kTileBytes);
         const uint32_t k_addr = smem_u32(k_smem + (size_t)stage * kTileBytes);
-        const uint32_t d = tmem_base + (buf ? kColS1 : kColS0);
+        const uint32_t d = tmem_base + kColS + t * 128;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
@@ -154,15 +169,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                      idesc_qk, ks > 0);
         }
       };
-      // O += P_j V_j: A = P from TMEM (two 16-bit values per column, 8 columns per step),
+      // O_t += P_t V_j: A = P from TMEM (two 16-bit values per column, 8 columns per step),
       // B = V_j in MN-major form: 64 head-dim values (128 bytes) are contiguous, 8 keys
       // make one 1024-byte swizzle atom (stride-dimension offset), the second 64-column
       // box sits kHalfBytes further (leading-dimension offset); a step of 16 keys is two
       // atoms = 2048 bytes
-      auto issue_pv = [&](int buf, int stage, bool accumulate) {
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t v_addr = smem_u32(v_smem + (size_t)stage * kTileBytes);
-        const uint32_t a = tmem_base + (buf ? kColS1 : kColS0);
-        const uint32_t d = tmem_base + kColO;
+        const uint32_t a = tmem_base + kColS + t * 128;
+        const uint32_t d = tmem_base + kColO + t * 128;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           tc::mma_ts(d, a + ks * 8, tc::smem_desc(v_addr + ks * 2048, kHalfBytes, 1024), idesc_pv,
@@ -173,126 +188,151 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok && n_kv > 0) ok = mbar_wait(&k_full[0], 0, &failed);
       if (ok && n_kv > 0) {
         tc::fence_after_sync();
-        issue_qk(0, 0);
-        tc::mma_commit(&s_full[0]);
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {
+          if (n_kv_t[t] > 0) {
+            issue_qk(t, 0);
+            tc::mma_commit(&s_full[t]);
+          }
+        }
         tc::mma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          const int s1 = (j + 1) & 1, n1 = (j + 1) >> 1;
-          ok = mbar_wait(&k_full[s1], n1 & 1, &failed);
-          // buffer s1 still holds P_{j-1} until O += P_{j-1} V_{j-1} has finished
-          if (ok && j >= 1) ok = mbar_wait(&pv_done[s1], ((j - 1) >> 1) & 1, &failed);
-          if (!ok) break;
-          tc::fence_after_sync();
-          issue_qk(s1, s1);
-          tc::mma_commit(&s_full[s1]);
-          tc::mma_commit(&k_empty[s1]);
-        }
         const int s = j & 1, n = j >> 1;
-        ok = mbar_wait(&p_full[s], n & 1, &failed);
-        if (ok) ok = mbar_wait(&v_full[s], n & 1, &failed);
+        const int s1 = (j + 1) & 1, n1 = (j + 1) >> 1;
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {
+          if (j < n_kv_t[t]) {
+            ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
+            ok = ok && mbar_wait(&v_full[s], n & 1, &failed);
+            if (!ok) break;
+            tc::fence_after_sync();
+            issue_pv(t, s, j > 0);
+            tc::mma_commit(&pv_done[t]);
+          }
+          if (j + 1 < n_kv_t[t]) {
+            // P_t(j) has been consumed by the MMAs just issued (the tensor core runs
+            // them in order), so tile t's buffer can take S_t(j+1)
+            ok = ok && mbar_wait(&k_full[s1], n1 & 1, &failed);
+            if (!ok) break;
+            tc::fence_after_sync();
+            issue_qk(t, s1);
+            tc::mma_commit(&s_full[t]);
+          }
+        }
         if (!ok) break;
-        tc::fence_after_sync();
-        issue_pv(s, s, j > 0);
-        tc::mma_commit(&pv_done[s]);
         tc::mma_commit(&v_empty[s]);
+        if (j + 1 < n_kv) tc::mma_commit(&k_empty[s1]);
       }
       if (!ok) failed = 1;
     }
     __syncwarp();
   } else {
     // ----------------------------------------------------------- softmax + epilogue
+    const int t = (warp - 2) >> 2;           // query tile of this warp group
     const int quad = warp & 3;               // TMEM lane quadrant this warp may touch
-    const int row = quad * 32 + lane;        // row of the query tile
-    const int qi = q0 + row;
+    const int row = quad * 32 + lane;        // row inside the query tile
+    const int qt0 = q0 + t * BM;
+    const int qi = qt0 + row;
+    const int my_n_kv = n_kv_t[t];
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + kColS + t * 128;
+    const uint32_t o_addr = lane_addr + kColO + t * 128;
     float m_used = -INFINITY;  // reference maximum (scaled, log2 domain)
     float l = 0.f;             // running sum of exp2(s - m_used)
     bool ok = true;
 
-    for (int j = 0; j < n_kv; ++j) {
-      const int s = j & 1, n = j >> 1;
-      if (!__all_sync(kFull, mbar_wait(&s_full[s], n & 1, &failed))) {
+    for (int j = 0; j < my_n_kv; ++j) {
+      if (!__all_sync(kFull, mbar_wait(&s_full[t], j & 1, &failed))) {
         ok = false;
         break;
       }
       tc::fence_after_sync();
-      const uint32_t s_addr = lane_addr + (s ? kColS1 : kColS0);
-      float v[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c)
-        tc::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
-      tc::tmem_wait_ld();
-
       const int col0 = j * BN;
-      const bool edge = (col0 + BN > p.Sk) || (p.causal && (col0 + BN - 1 > q0 + diag));
-      float mx = -INFINITY;
+      const bool edge = (col0 + BN > p.Sk) || (p.causal && (col0 + BN - 1 > qt0 + diag));
+      // last visible key of this row, relative to the tile
+      int lim = BN - 1;
       if (edge) {
-        const int lim = p.causal ? (qi + diag < p.Sk - 1 ? qi + diag : p.Sk - 1) : p.Sk - 1;
+        int last = p.Sk - 1;
+        if (p.causal && qi + diag < last) last = qi + diag;
+        lim = last - col0;
+      }
+      // ---- pass 1: row maximum of the raw scores
+      float mx = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          v[c] = (col0 + c <= lim) ? v[c] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, v[c]);
-        }
-      } else {
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tc::tmem_ld32(s_addr + c * 32, raw);
+        tc::tmem_wait_ld();
+        if (edge) {
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          v[c] *= p.scale_log2;
-          mx = fmaxf(mx, v[c]);
+          for (int e = 0; e < 32; ++e)
+            mx = fmaxf(mx, (c * 32 + e <= lim) ? __uint_as_float(raw[e]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            mx = max3(mx, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
         }
       }
+      mx *= p.scale_log2;  // scale > 0: scaling commutes with the maximum
       // lazy rescale: move the reference maximum only when it would grow by > 2^8
       const bool grow = mx > m_used + kRescaleThreshold;  // also true for the first tile
       if (__any_sync(kFull, grow)) {
         const float m_new = grow ? mx : m_used;
-        const float factor = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-        l *= grow ? factor : 1.f;
+        const float f = !grow ? 1.f : ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new));
+        l *= f;
         if (j > 0) {
-          // O may only be touched once O += P_{j-1} V_{j-1} has completed
-          if (!__all_sync(kFull, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, &failed))) {
+          // O may only be touched once O += P(j-1) V(j-1) has completed
+          if (!__all_sync(kFull, mbar_wait(&pv_done[t], (j - 1) & 1, &failed))) {
             ok = false;
             break;
           }
           tc::fence_after_sync();
-          const float f = grow ? factor : 1.f;
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t o[32];
-            tc::tmem_ld32(lane_addr + kColO + c * 32, o);
+            tc::tmem_ld32(o_addr + c * 32, o);
             tc::tmem_wait_ld();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-            tc::tmem_st32(lane_addr + kColO + c * 32, o);
+            tc::tmem_st32(o_addr + c * 32, o);
           }
           tc::tmem_wait_st();
         }
         m_used = m_new;
       }
+      // ---- pass 2: P = exp2(s * scale - m_used), 32 columns at a time
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
-      uint32_t pk[BN / 2];
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-mref, -mref);
+      float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < BN; c += 2) {
-        const float p0 = fast_exp2(v[c] - mref);
-        const float p1 = fast_exp2(v[c + 1] - mref);
-        sum += p0 + p1;
-        pk[c / 2] = pack_pair(p0, p1, IS_BF16);
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tc::tmem_ld32(s_addr + c * 32, raw);
+        tc::tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float2 a = fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2, nm2);
+          float2 pe = make_float2(fast_exp2(a.x), fast_exp2(a.y));
+          if (edge) {
+            if (c * 32 + e > lim) pe.x = 0.f;
+            if (c * 32 + e + 1 > lim) pe.y = 0.f;
+          }
+          sum2 = add2(sum2, pe);
+          pk[e / 2] = pack_pair(pe.x, pe.y, IS_BF16);
+        }
+        // P columns [16c, 16c+16) lie inside S columns already read (<= 32c+31)
+        tc::tmem_st16(s_addr + c * 16, pk);
       }
-      l += sum;
-      // P_j overwrites the first 64 columns of the S buffer it came from
-#pragma unroll
-      for (int c = 0; c < BN / 64; ++c)
-        tc::tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
+      l += sum2.x + sum2.y;
       tc::tmem_wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(&p_full[s]);
+      tc::mbar_arrive(&p_full[t]);
     }
 
-    if (ok && n_kv > 0) {
-      const int jl = n_kv - 1;
-      ok = mbar_wait(&pv_done[jl & 1], (jl >> 1) & 1, &failed);
-    }
+    if (ok && my_n_kv > 0) ok = mbar_wait(&pv_done[t], (my_n_kv - 1) & 1, &failed);
     ok = __all_sync(kFull, ok);
     if (ok) {
       tc::fence_after_sync();
@@ -301,31 +341,28 @@ __global__ void __launch_bounds__(kThreads, 1)
       unsigned char* orow = reinterpret_cast<unsigned char*>(p.o) +
                             2 * ((long long)b * p.o_stride_b + (long long)h * p.o_stride_h +
                                  (long long)qi * p.o_stride_s);
+      if (my_n_kv > 0) {
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t o[32];
-        if (n_kv > 0) {
-          tc::tmem_ld32(lane_addr + kColO + c * 32, o);
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tc::tmem_ld32(o_addr + c * 32, o);
           tc::tmem_wait_ld();
-        } else {
+          if (live) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0;
-        }
-        if (live) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 w;
-            w.x = pack_pair(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv, IS_BF16);
-            w.y = pack_pair(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv, IS_BF16);
-            w.z = pack_pair(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv, IS_BF16);
-            w.w = pack_pair(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv, IS_BF16);
-            *reinterpret_cast<uint4*>(orow + (c * 32 + e) * 2) = w;
+            for (int e = 0; e < 32; e += 8) {
+              uint4 w;
+              w.x = pack_pair(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv, IS_BF16);
+              w.y = pack_pair(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv, IS_BF16);
+              w.z = pack_pair(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv, IS_BF16);
+              w.w = pack_pair(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv, IS_BF16);
+              *reinterpret_cast<uint4*>(orow + (c * 32 + e) * 2) = w;
+            }
           }
         }
-      }
-      if (live && p.lse != nullptr) {
-        const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.69314718055994530942f : -INFINITY;
-        p.lse[((long long)b * p.H + h) * p.Sq + qi] = lse;
+        if (live && p.lse != nullptr) {
+          const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.69314718055994530942f : -INFINITY;
+          p.lse[((long long)b * p.H + h) * p.Sq + qi] = lse;
+        }
       }
     } else {
       failed = 1;
@@ -417,7 +454,8 @@ extern "C" int ixb_fa_fwd(int dtype, const void* q, const void* k, const void* v
   p.Sk = Sk;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal ? 1 : 0;
-  const dim3 grid((Sq + BM - 1) / BM, B * H);
+  if (!(scale > 0.f)) return IXB_ERR_ARG;  // the row maximum is taken before scaling
+  const dim3 grid((Sq + BM * NQ - 1) / (BM * NQ), B * H);
   auto kern = is_bf16 ? fa_fwd_kernel<true> : fa_fwd_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return ixb_host::cuda_status(e);

@@ -1,6 +1,7 @@
 """GPU parity tests of the fused-attention kernel (tcgen05 / TMEM / TMA) through the C ABI.
 
-Tolerance: 2e-2 relative to max(|expected|, rms(expected)) for fp16 / bf16 outputs;
+Tolerance: 2e-2 relative to max(|expected|, rms of the expected row) for fp16 / bf16
+outputs (rows of a causal output differ in scale, so each is judged on its own);
 log-sum-exp within 2e-3 absolute (it is accumulated in fp32)."""
 import math
 
@@ -27,17 +28,17 @@ def run(d, cuda, causal, **kw):
 def test_attention_vs_oracle(cuda, dtype, causal, B, H, S):
     d = inputs.c4(B, H, S, 128, seed=B * 100 + S, dtype=dtype)
     out, lse = run(d, cuda, causal)
-    exp, else = graphs.attention(d["q"], d["k"], d["v"], d["scale"], causal=causal)
-    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
-    assert float((lse.cpu() - else).abs().max()) <= 2e-3
+    exp, elog = graphs.attention(d["q"], d["k"], d["v"], d["scale"], causal=causal)
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
+    assert float((lse.cpu() - elog).abs().max()) <= 2e-3
 
 
 def test_attention_vs_c_oracle_small(cuda):
     d = inputs.c4(1, 2, 160, 128, seed=9)
     out, lse = run(d, cuda, True)
-    exp, else = c_oracle.attention(d["q"], d["k"], d["v"], d["scale"], causal=True)
-    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
-    assert float((lse.cpu().double() - else).abs().max()) <= 2e-3
+    exp, elog = c_oracle.attention(d["q"], d["k"], d["v"], d["scale"], causal=True)
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
+    assert float((lse.cpu().double() - elog).abs().max()) <= 2e-3
 
 
 def test_attention_cross_lengths(cuda):
@@ -50,7 +51,7 @@ def test_attention_cross_lengths(cuda):
     for causal in (False, True):
         out = ops.fused_attention(q.to(cuda), k.to(cuda), v.to(cuda), sc, causal=causal, check=True)
         exp, _ = graphs.attention(q, k, v, sc, causal=causal)
-        assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+        assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
 
 
 def test_attention_transposed_layout_no_copy(cuda):
@@ -62,7 +63,7 @@ def test_attention_transposed_layout_no_copy(cuda):
     assert not qd.is_contiguous()
     out = ops.fused_attention(qd, kd, vd, 0.1, causal=False, check=True)
     exp = graphs.attention_pattern(q.float(), k.float(), v.float(), 10.0)
-    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
 
 
 def test_attention_reference_pattern_golden(cuda, golden):
@@ -71,7 +72,7 @@ def test_attention_reference_pattern_golden(cuda, golden):
     exp = graphs.attention_pattern(p["query"], p["key"], p["value"], p["inv_scale_factor"])
     q, k, v = (p[n].bfloat16().to(cuda).transpose(1, 2) for n in ("query", "key", "value"))
     out = ops.fused_attention(q, k, v, 1.0 / p["inv_scale_factor"], causal=False, check=True)
-    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
 
 
 def test_attention_large_scores_rescale_path(cuda):
@@ -83,9 +84,9 @@ def test_attention_large_scores_rescale_path(cuda):
     q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
     out, lse = ops.fused_attention(q.to(cuda), k.to(cuda), v.to(cuda), 1.0, causal=False,
                                    return_lse=True, check=True)
-    exp, else = graphs.attention(q, k, v, 1.0, causal=False)
-    assert graphs.max_rel_err(out.cpu(), exp) <= TOL
-    assert float((lse.cpu() - else).abs().max()) <= 5e-3 * float(else.abs().max())
+    exp, elog = graphs.attention(q, k, v, 1.0, causal=False)
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= TOL
+    assert float((lse.cpu() - elog).abs().max()) <= 5e-3 * float(elog.abs().max())
 
 
 def test_attention_full_size_rows_vs_golden(cuda, golden):
@@ -94,7 +95,7 @@ def test_attention_full_size_rows_vs_golden(cuda, golden):
     rows = golden["c4_rows"].tolist()
     for i, (b, h) in enumerate(golden["c4_heads"].tolist()):
         got = out[b, h][rows].cpu()
-        assert graphs.max_rel_err(got, golden["c4_out_rows"][i]) <= TOL
+        assert graphs.max_rel_err(got, golden["c4_out_rows"][i], dim=-1) <= TOL
         assert float((lse[b, h][rows].cpu() - golden["c4_lse_rows"][i]).abs().max()) <= 2e-3
     # size-independent property: causal row 0 attends to key 0 only -> out[0] == v[0]
     assert torch.equal(out[:, :, 0].cpu(), d["v"][:, :, 0])
