@@ -457,6 +457,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--c4-batch", type=int, default=0,
+                    help="override the attention batch (profiling captures on a smaller case)")
     args = ap.parse_args()
     wl_cls = WORKLOADS[args.workload]
 
@@ -481,6 +483,9 @@ def main():
     rt.load()
     peaks = measured_peaks()
     wl = wl_cls()
+    if args.c4_batch > 0 and isinstance(wl, FusedAttention):
+        wl.B = args.c4_batch
+        wl.name = wl.name.replace("_b8_", f"_b{args.c4_batch}_")
     wl.setup(device, seed=rank)  # each rank owns a different shard of the global batch
 
     sampler = ClockSampler(local_rank)

@@ -257,20 +257,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (p.causal && qi + diag < last) last = qi + diag;
         lim = last - col0;
       }
-      // ---- pass 1: row maximum of the raw scores
+      // ---- pass 1: row maximum of the raw scores, two 64-column round trips
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t raw[32];
-        tc::tmem_ld32(s_addr + c * 32, raw);
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t raw[64];
+        tc::tmem_ld32(s_addr + hh * 64, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+        tc::tmem_ld32(s_addr + hh * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
         tc::tmem_wait_ld();
         if (edge) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            mx = fmaxf(mx, (c * 32 + e <= lim) ? __uint_as_float(raw[e]) : -INFINITY);
+          for (int e = 0; e < 64; ++e)
+            mx = fmaxf(mx, (hh * 64 + e <= lim) ? __uint_as_float(raw[e]) : -INFINITY);
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2)
+          for (int e = 0; e < 64; e += 2)
             mx = max3(mx, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
         }
       }
@@ -301,29 +302,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         m_used = m_new;
       }
-      // ---- pass 2: P = exp2(s * scale - m_used), 32 columns at a time
+      // ---- pass 2: P = exp2(s * scale - m_used); the next 32 columns are requested
+      // before the current 32 are processed so the TMEM latency overlaps the arithmetic
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nm2 = make_float2(-mref, -mref);
       float2 sum2 = make_float2(0.f, 0.f);
+      uint32_t buf[2][32];
+      tc::tmem_ld32(s_addr, buf[0]);
+      tc::tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
-        uint32_t raw[32];
-        tc::tmem_ld32(s_addr + c * 32, raw);
-        tc::tmem_wait_ld();
+        const uint32_t(&raw)[32] = buf[c & 1];
+        // P columns [16c, 16c+16) hold S columns that are already in registers, and the
+        // prefetch below reads S columns [32c+32, 32c+64): no overlap with the store
+        if (c + 1 < BN / 32) tc::tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const float2 a = fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2, nm2);
+          const int col = c * 32 + e;
+          const float2 a =
+              fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2, nm2);
           float2 pe = make_float2(fast_exp2(a.x), fast_exp2(a.y));
           if (edge) {
-            if (c * 32 + e > lim) pe.x = 0.f;
-            if (c * 32 + e + 1 > lim) pe.y = 0.f;
+            if (col > lim) pe.x = 0.f;
+            if (col + 1 > lim) pe.y = 0.f;
           }
           sum2 = add2(sum2, pe);
           pk[e / 2] = pack_pair(pe.x, pe.y, IS_BF16);
         }
-        // P columns [16c, 16c+16) lie inside S columns already read (<= 32c+31)
+        tc::tmem_wait_ld();
         tc::tmem_st16(s_addr + c * 16, pk);
       }
       l += sum2.x + sum2.y;

@@ -32,16 +32,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One attempt: the thread may be suspended by the hardware for up to `suspend_ns`
+// nanoseconds waiting for the phase, so a waiting warp does not burn issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity,
+                                              uint32_t suspend_ns = 1000000u) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
       : "memory");
   return ok != 0;
 }
@@ -49,7 +52,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // `abort` (a flag another role of the CTA raises when its own wait gave up) is non-zero.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           const volatile int* abort = nullptr) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int quick = 0; quick < 64; ++quick)
+    if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
