@@ -18,7 +18,8 @@ from typing import Optional
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libixb.so")
+# IXB_LIB_PATH points at an alternative build of the library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("IXB_LIB_PATH") or os.path.join(_PKG_DIR, "libixb.so")
 
 IXB_OK = 0
 IXB_ERR_ARG, IXB_ERR_DTYPE, IXB_ERR_ALIGN, IXB_ERR_SHAPE = 1, 2, 3, 4
