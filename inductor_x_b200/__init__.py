@@ -1,12 +1,100 @@
 """inductor_x_b200 - a B200 (sm_100a) TorchInductor backend.
 
 Drop-in for the registration surface of BD-Seed-HHW/inductor-x (imported there as
-``inductor_npu``): importing the package registers the backend for CUDA devices, the way
-``inductor_x/__init__.py:16-58`` does for ``"npu"``.  Underneath, kernels come from
-hand-written CUDA templates in ``libixb.so`` instead of generated Triton.
+``inductor_npu``).  Importing the package does for ``"cuda"`` what
+``inductor_x/__init__.py:16-63`` does for ``"npu"``:
+
+* registers the scheduling and wrapper classes (``_inductor_register_backend_for_device``),
+* registers device-op overrides so that generated wrappers import
+  ``get_current_raw_stream`` from this package (``NewNPUDeviceOpOverrides``),
+* registers the Dynamo device interface (``NewNpuInterface``),
+* applies the lowering policy and decomposition edits, and
+* registers the fused-attention FX pattern.
+
+After that ``torch.compile(fn)`` on CUDA tensors emits no Triton: every fused group becomes
+an instantiation of a hand-written CUDA template, compiled once and called through the C ABI.
+Set ``IXB_REGISTER=0`` to import the kernels (``inductor_x_b200.ops``) without touching
+Inductor.
 """
+import torch
+
+from . import config  # noqa: F401
 from . import runtime  # noqa: F401
 from . import ops  # noqa: F401
-from .runtime import raw_stream as get_current_raw_stream  # noqa: F401
 
-__all__ = ["ops", "runtime", "get_current_raw_stream"]
+
+def get_current_raw_stream(device=None) -> int:
+    """Raw handle of the current CUDA stream (``inductor_x/__init__.py:26-27``)."""
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+_registered = False
+
+
+def _inductor_register_backend_for_device():
+    from torch._inductor.codegen.common import register_backend_for_device
+
+    from .codegen import B200Scheduling, B200WrapperCodeGen
+    from .fusion_attention_graph import B200AttentionPass
+
+    register_backend_for_device("cuda", B200Scheduling, B200WrapperCodeGen,
+                                device_custom_pass=B200AttentionPass())
+
+
+def _inductor_register_device_op_overrides():
+    from torch._inductor.codegen.common import register_device_op_overrides
+    from torch._inductor.codegen.cuda.device_op_overrides import CUDADeviceOpOverrides
+
+    class B200DeviceOpOverrides(CUDADeviceOpOverrides):
+        def import_get_raw_stream_as(self, name):
+            return f"from inductor_x_b200 import get_current_raw_stream as {name}"
+
+    register_device_op_overrides("cuda", B200DeviceOpOverrides())
+
+
+def _register_device_interface():
+    from torch._dynamo.device_interface import CudaInterface, register_interface_for_device
+
+    class B200Interface(CudaInterface):
+        @staticmethod
+        def is_available() -> bool:
+            return torch.cuda.is_available() and torch.cuda.device_count() > 0
+
+        @staticmethod
+        def is_triton_capable(device=None) -> bool:
+            # generated kernels come from CUDA templates; Triton is never asked to compile
+            return True
+
+        @staticmethod
+        def raise_if_triton_unavailable(device=None) -> None:
+            return None
+
+    register_interface_for_device("cuda", B200Interface)
+
+
+def register():
+    """Perform the registrations (idempotent).  Called at import unless IXB_REGISTER=0."""
+    global _registered
+    if _registered:
+        return
+    from torch._inductor import lowering as inductor_lowering
+
+    from .decomposition import _register_b200_inductor_decompositions
+    from .lowering import _register_b200_inductor_fallbacks, make_reduction
+
+    _inductor_register_backend_for_device()
+    _inductor_register_device_op_overrides()
+    _register_device_interface()
+    inductor_lowering.make_reduction = make_reduction
+    _register_b200_inductor_fallbacks()
+    _register_b200_inductor_decompositions()
+    from . import fusion_attention_graph
+
+    fusion_attention_graph.register_fx_pass()
+    _registered = True
+
+
+if config.register_on_import:
+    register()
+
+__all__ = ["ops", "runtime", "config", "get_current_raw_stream", "register"]

@@ -1,0 +1,126 @@
+"""Index-expression analysis for the template instantiator.
+
+Inductor hands a kernel flattened iteration ranges and index expressions written with
+``FloorDiv`` / ``ModularIndexing`` of those flat variables.  The reference recovers the
+true axes by rewriting such pairs into real loop variables
+(``inductor_x/codegen/ir.py:26-146``: ``detect_flattened_dims``, ``rebuild_flattened_dims``,
+``substituted_dims_in_indexing``) and then looks for the axes that are stride-1 in some
+access (``find_lowest_dimension``, ``inductor_x/codegen/split_tiling.py:188-239``).  The
+CUDA templates need the same two facts in a different form:
+
+* is an access *contiguous along the flat vector a thread owns* (128-bit access), and
+* is an access *contiguous along the reduced row* (row template) - and if not, what is the
+  stride of the reduced variable (outer reduction).
+
+Both are answered on the expression expanded back to the root index variables, by exact
+integer evaluation at sample points (the expressions are piecewise-affine in the roots, so
+sampled agreement on aligned groups is decisive for the static shapes handled here).
+"""
+from __future__ import annotations
+
+import random
+from typing import Dict, Iterable, Optional, Sequence
+
+import sympy
+
+
+def expand_to_roots(index: sympy.Expr, range_tree_nodes: Dict[sympy.Symbol, object]) -> sympy.Expr:
+    """Rewrite ``index`` so that only root index symbols (``xindex``, ``r0_index`` ...) and
+    non-range symbols remain.  ``range_tree_nodes`` maps entry symbols to entries whose
+    ``.expr`` is written in terms of their root symbol."""
+    for _ in range(8):
+        syms = [s for s in index.free_symbols if s in range_tree_nodes]
+        if not syms:
+            break
+        index = index.subs({s: range_tree_nodes[s].expr for s in syms})
+    return index
+
+
+def _eval(expr: sympy.Expr, env: Dict[sympy.Symbol, int]) -> Optional[int]:
+    try:
+        v = expr.subs(env)
+        return int(v) if v.is_Integer else None
+    except Exception:
+        return None
+
+
+def _sample_bases(numel: int, group: int, n: int = 12) -> Iterable[int]:
+    groups = max(numel // group, 1)
+    rnd = random.Random(1234)
+    picks = {0, 1, 2, groups - 1, groups // 2, groups // 3}
+    while len(picks) < min(n, groups):
+        picks.add(rnd.randrange(groups))
+    return [g * group for g in sorted(picks) if 0 <= g < groups]
+
+
+def is_vector_contiguous(expr: sympy.Expr, root: sympy.Symbol, vec: int, numel: int) -> bool:
+    """True when, for every flat position b that is a multiple of ``vec``,
+    ``expr(b + k) == expr(b) + k`` for k < vec: the ``vec`` elements a thread owns are
+    adjacent in memory.  ``expr`` must contain no symbol other than ``root``."""
+    if expr.free_symbols - {root}:
+        return False
+    if numel < vec:
+        return False
+    for b in _sample_bases(numel, vec):
+        if b + vec > numel:
+            continue
+        base = _eval(expr, {root: b})
+        if base is None:
+            return False
+        for k in range(1, vec):
+            if _eval(expr, {root: b + k}) != base + k:
+                return False
+    return True
+
+
+def reduction_stride(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol, xnumel: int,
+                     rnumel: int) -> Optional[int]:
+    """Stride of the flat reduction variable in ``expr`` if it is one constant over the
+    whole range (``expr(x, r) == expr(x, 0) + stride * r``), else None.  Stride 1 means the
+    access walks the row contiguously (row template); a larger constant stride means an
+    outer reduction; None means the reduced range is itself a flattening of several axes
+    with different strides."""
+    if expr.free_symbols - {x_root, r_root}:
+        return None
+    if r_root not in expr.free_symbols:
+        return 0
+    xs = sorted({0, 1, xnumel - 1, xnumel // 2, xnumel // 3} & set(range(xnumel)))
+    rs = sorted({1, 2, 3, rnumel - 1, rnumel // 2, rnumel // 3 + 1} & set(range(1, rnumel)))
+    stride = None
+    for x in xs:
+        base = _eval(expr, {x_root: x, r_root: 0})
+        if base is None:
+            return None
+        for r in rs:
+            v = _eval(expr, {x_root: x, r_root: r})
+            if v is None or (v - base) % r != 0:
+                return None
+            s = (v - base) // r
+            if stride is None:
+                stride = s
+            elif s != stride:
+                return None
+    return stride if stride is not None else (1 if rnumel == 1 else None)
+
+
+def x_stride_at_row_start(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol,
+                          xnumel: int) -> Optional[int]:
+    """For a row-contiguous access: distance between the starts of consecutive rows, if it
+    is constant (it is ``rnumel`` for a dense operand, 0 for a broadcast row vector)."""
+    if xnumel <= 1:
+        return 0
+    env0 = {r_root: 0}
+    base = _eval(expr, {**env0, x_root: 0})
+    if base is None:
+        return None
+    s = None
+    for x in sorted({1, 2, xnumel - 1, xnumel // 2} & set(range(1, xnumel))):
+        v = _eval(expr, {**env0, x_root: x})
+        if v is None or (v - base) % x != 0:
+            return None
+        cur = (v - base) // x
+        if s is None:
+            s = cur
+        elif cur != s:
+            return None
+    return s

@@ -1,0 +1,379 @@
+"""Fused-attention graph pass: SDPA-shaped subgraphs -> the tcgen05 flash-attention kernel.
+
+Surface kept from ``inductor_x/npu_fusion_attention_graph.py``:
+
+* custom ops ``<ns>::b200_fa`` / ``b200_fa_backward`` with the reference's 19-argument /
+  27-argument schemas (``:13-18``), a CUDA implementation (``:20-42``) and a Meta
+  implementation (``:45-86``);
+* the autograd wrapper and public entry ``b200_fusion_attention_graph`` (``:88-132``);
+* ``register_fx_pass`` registering the reference's search pattern - permute x3,
+  ``matmul . div(inv_scale) . softmax . dropout . matmul`` - in training and inference
+  variants into ``joint_graph.patterns`` (``:134-230``).
+
+Additions the benchmark graphs need and the reference lacks (its only pattern has no mask):
+a device graph pass that retargets ``aten._scaled_dot_product_*_attention`` nodes - what
+``F.scaled_dot_product_attention(..., is_causal=True)`` and the stock causal-mask patterns
+become - to the same kernel.
+
+Scale convention: as in the reference, the op's ``scale`` argument carries
+``inv_scale_factor`` and the implementation inverts it before calling the kernel
+(``:22-29,162``).  ``softmax_max`` / ``softmax_sum`` are returned as ``(logsumexp, 1)``
+broadcast to ``[B, N, S, 8]``: an equivalent (max, sum) pair for ``exp(s - max) / sum``.
+"""
+from __future__ import annotations
+
+import functools
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch.autograd import Function
+from torch.library import Library
+
+TOKEN_MAX = 2147483647
+NAMESPACE = "b200_graph"
+
+b200_def = Library(NAMESPACE, "DEF")
+b200_def.define(
+    "b200_fa(Tensor query, Tensor key, Tensor value, int head_num, str input_layout, Tensor? pse=None, "
+    "Tensor? padding_mask=None, Tensor? atten_mask=None, float scale=1., float keep_prob=1., "
+    "int pre_tockens=2147483647, int next_tockens=2147483647, int inner_precise=0, int[]? prefix=None, "
+    "int[]? actual_seq_qlen=None, int[]? actual_seq_kvlen=None, int sparse_mode=0, "
+    "bool gen_mask_parallel=True, bool sync=False) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+b200_def.define(
+    "b200_fa_backward(Tensor query, Tensor key, Tensor value, Tensor dy, int head_num, str input_layout, *, "
+    "Tensor? pse=None, Tensor? padding_mask=None, Tensor? atten_mask=None, Tensor? softmax_max=None, "
+    "Tensor? softmax_sum=None, Tensor? softmax_in=None, Tensor? attention_in=None, float scale_value=1., "
+    "float keep_prob=1., int pre_tockens=2147483647, int next_tockens=2147483647, int inner_precise=0, "
+    "Tensor? seed=None, Tensor? offset=None, Tensor? numels=None, int[]? prefix=None, "
+    "int[]? actual_seq_qlen=None, int[]? actual_seq_kvlen=None, int sparse_mode=0, "
+    "bool gen_mask_parallel=True, bool sync=False) -> (Tensor, Tensor, Tensor, Tensor)")
+# compact form used by the SDPA retargeting pass: (out, logsumexp)
+b200_def.define("b200_sdpa(Tensor query, Tensor key, Tensor value, float scale, bool is_causal) -> (Tensor, Tensor)")
+
+b200_cuda = Library(NAMESPACE, "IMPL", "CUDA")
+b200_meta = Library(NAMESPACE, "IMPL", "Meta")
+
+CAUSAL_SPARSE_MODES = (2, 3)  # left-up / right-down aligned causal masks
+
+
+def _to_bnsd(t: torch.Tensor, layout: str, head_num: int) -> torch.Tensor:
+    if layout == "BNSD":
+        return t
+    if layout == "BSND":
+        return t.transpose(1, 2)
+    if layout == "BSH":
+        b, s, h = t.shape
+        return t.view(b, s, head_num, h // head_num).transpose(1, 2)
+    if layout == "SBH":
+        s, b, h = t.shape
+        return t.view(s, b, head_num, h // head_num).permute(1, 2, 0, 3)
+    raise ValueError(f"unsupported input_layout {layout!r}")
+
+
+def _from_bnsd(t: torch.Tensor, layout: str) -> torch.Tensor:
+    if layout == "BNSD":
+        return t
+    if layout == "BSND":
+        return t.transpose(1, 2).contiguous()
+    b, n, s, d = t.shape
+    if layout == "BSH":
+        return t.transpose(1, 2).reshape(b, s, n * d)
+    return t.permute(2, 0, 1, 3).reshape(s, b, n * d)
+
+
+def _run_kernel(q, k, v, scale: float, causal: bool):
+    from . import ops
+
+    dt = q.dtype
+    if dt == torch.float32:  # the reference traces its pattern in fp32 only (:174)
+        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if k.stride(-1) != 1:
+        k = k.contiguous()
+    if v.stride(-1) != 1:
+        v = v.contiguous()
+    out, lse = ops.fused_attention(q, k, v, scale, causal=causal, return_lse=True)
+    return out.to(dt), lse
+
+
+def b200_fa_impl(query, key, value, head_num, input_layout, pse=None, padding_mask=None,
+                 atten_mask=None, scale=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX, next_tockens=TOKEN_MAX,
+                 inner_precise=0, prefix=None, actual_seq_qlen=None, actual_seq_kvlen=None, sparse_mode=0,
+                 gen_mask_parallel=True, sync=False):
+    if pse is not None or padding_mask is not None or keep_prob != 1.0:
+        raise NotImplementedError("b200_fa: pse, padding_mask and dropout are not supported")
+    causal = sparse_mode in CAUSAL_SPARSE_MODES
+    if atten_mask is not None and not causal:
+        raise NotImplementedError("b200_fa: only causal masks (sparse_mode 2 or 3) are supported")
+    q = _to_bnsd(query, input_layout, head_num)
+    k = _to_bnsd(key, input_layout, head_num)
+    v = _to_bnsd(value, input_layout, head_num)
+    if sparse_mode == 2 and q.shape[2] != k.shape[2]:
+        raise NotImplementedError("b200_fa: left-up causal needs equal sequence lengths")
+    # the op receives inv_scale_factor; the kernel wants the multiplier
+    out, lse = _run_kernel(q, k, v, 1.0 / scale, causal)
+    b, n, s, _ = out.shape
+    smax = lse.unsqueeze(-1).expand(b, n, s, 8).contiguous()
+    ssum = torch.ones_like(smax)
+    zero = lambda: torch.zeros(1, dtype=torch.int64)
+    return (_from_bnsd(out, input_layout), smax, ssum, torch.empty(0, dtype=query.dtype, device=query.device),
+            zero(), zero(), zero())
+
+
+def b200_fa_meta(query, key, value, head_num, input_layout, pse=None, padding_mask=None, atten_mask=None,
+                 scale=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX, next_tockens=TOKEN_MAX, inner_precise=0,
+                 prefix=None, actual_seq_qlen=None, actual_seq_kvlen=None, sparse_mode=0,
+                 gen_mask_parallel=True, sync=False):
+    if input_layout == "BSH":
+        b, s1 = query.size(0), query.size(1)
+    elif input_layout == "SBH":
+        b, s1 = query.size(1), query.size(0)
+    elif input_layout == "BSND":
+        b, s1 = query.size(0), query.size(1)
+    else:
+        b, s1 = query.size(0), query.size(2)
+    stats = torch.empty([b, head_num, s1, 8], dtype=torch.float32, device="meta")
+    return (torch.empty_like(query, device="meta").contiguous(), stats, torch.empty_like(stats),
+            torch.empty([0], dtype=query.dtype, device="meta"),
+            torch.empty([1], dtype=torch.int64, device="meta"),
+            torch.empty([1], dtype=torch.int64, device="meta"),
+            torch.empty([1], dtype=torch.int64, device="meta"))
+
+
+def b200_fa_backward_impl(*args, **kwargs):
+    raise NotImplementedError("b200_fa_backward: the attention backward kernel is not built yet")
+
+
+def b200_fa_backward_meta(query, key, value, dy, head_num, input_layout, **kwargs):
+    pse = kwargs.get("pse")
+    return (torch.empty_like(query, device="meta"), torch.empty_like(key, device="meta"),
+            torch.empty_like(value, device="meta"),
+            torch.empty([0], dtype=query.dtype, device="meta") if pse is not None else None)
+
+
+def b200_sdpa_impl(query, key, value, scale, is_causal):
+    return _run_kernel(query, key, value, scale, is_causal)
+
+
+def b200_sdpa_meta(query, key, value, scale, is_causal):
+    b, n, s, d = query.shape
+    return (torch.empty((b, n, s, d), dtype=query.dtype, device="meta"),
+            torch.empty((b, n, s), dtype=torch.float32, device="meta"))
+
+
+b200_cuda.impl("b200_fa", b200_fa_impl)
+b200_meta.impl("b200_fa", b200_fa_meta)
+b200_cuda.impl("b200_fa_backward", b200_fa_backward_impl)
+b200_meta.impl("b200_fa_backward", b200_fa_backward_meta)
+b200_cuda.impl("b200_sdpa", b200_sdpa_impl)
+b200_meta.impl("b200_sdpa", b200_sdpa_meta)
+
+
+class B200GraphAttentionFunction(Function):
+    """Autograd wrapper (``NpuGraphAttentionFunction``, ``:88-123``).  Forward only for now:
+    backward raises until the backward kernel exists."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, head_num, input_layout, pse=None, padding_mask=None,
+                atten_mask=None, scale=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX, next_tockens=TOKEN_MAX,
+                inner_precise=0, prefix=None, actual_seq_qlen=None, actual_seq_kvlen=None, sparse_mode=0,
+                gen_mask_parallel=True, sync=False):
+        res = torch.ops.b200_graph.b200_fa(
+            query, key, value, head_num, input_layout, pse=pse, padding_mask=padding_mask,
+            atten_mask=atten_mask, scale=scale, keep_prob=keep_prob, pre_tockens=pre_tockens,
+            next_tockens=next_tockens, inner_precise=inner_precise, prefix=prefix,
+            actual_seq_qlen=actual_seq_qlen, actual_seq_kvlen=actual_seq_kvlen, sparse_mode=sparse_mode,
+            gen_mask_parallel=gen_mask_parallel, sync=sync)
+        ctx.save_for_backward(query, key, value, res[1], res[2], res[0])
+        ctx.head_num, ctx.input_layout, ctx.scale = head_num, input_layout, scale
+        ctx.sparse_mode = sparse_mode
+        return res
+
+    @staticmethod
+    def backward(ctx, *grads):
+        query, key, value, smax, ssum, out = ctx.saved_tensors
+        dq, dk, dv, _ = torch.ops.b200_graph.b200_fa_backward(
+            query, key, value, grads[0], ctx.head_num, ctx.input_layout, softmax_max=smax,
+            softmax_sum=ssum, attention_in=out, scale_value=ctx.scale, sparse_mode=ctx.sparse_mode)
+        return (dq, dk, dv) + (None,) * 16
+
+
+def b200_fusion_attention_graph(query, key, value, head_num, input_layout, pse=None, padding_mask=None,
+                                atten_mask=None, scale=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX,
+                                next_tockens=TOKEN_MAX, inner_precise=0, prefix=None, actual_seq_qlen=None,
+                                actual_seq_kvlen=None, sparse_mode=0, gen_mask_parallel=True, sync=False):
+    """Public entry (the reference installs it as ``torch_npu.npu_fusion_attention_graph``)."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
+        return B200GraphAttentionFunction.apply(
+            query, key, value, head_num, input_layout, pse, padding_mask, atten_mask, scale, keep_prob,
+            pre_tockens, next_tockens, inner_precise, prefix, actual_seq_qlen, actual_seq_kvlen,
+            sparse_mode, gen_mask_parallel, sync)
+    return torch.ops.b200_graph.b200_fa(
+        query, key, value, head_num, input_layout, pse=pse, padding_mask=padding_mask, atten_mask=atten_mask,
+        scale=scale, keep_prob=keep_prob, pre_tockens=pre_tockens, next_tockens=next_tockens,
+        inner_precise=inner_precise, prefix=prefix, actual_seq_qlen=actual_seq_qlen,
+        actual_seq_kvlen=actual_seq_kvlen, sparse_mode=sparse_mode, gen_mask_parallel=gen_mask_parallel,
+        sync=sync)
+
+
+# ---------------------------------------------------------------------------------------
+# FX pattern: the reference's search / replace pair, registered the reference's way
+# ---------------------------------------------------------------------------------------
+def _b200_fusion_attention_graph_pattern_1(query, key, value, inv_scale_factor, dropout_p):
+    q = query.permute(0, 2, 1, 3)
+    k = key.permute(0, 2, 1, 3)
+    v = value.permute(0, 2, 1, 3)
+    return torch.nn.functional.dropout(
+        torch.matmul(q, k.transpose(-2, -1)).div(inv_scale_factor).softmax(dim=-1),
+        p=dropout_p,
+    ).matmul(v)
+
+
+def _b200_fusion_attention_graph_replacement_1(query, key, value, inv_scale_factor, dropout_p):
+    from torch._dynamo.utils import counters
+
+    counters["inductor"]["fuse_attention"] += 1
+    head_num = query.size(2)
+    return b200_fusion_attention_graph(
+        query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), head_num, "BNSD", None,
+        atten_mask=None, scale=inv_scale_factor, keep_prob=1.0 - dropout_p)[0]
+
+
+def _pattern_extra_check(match) -> bool:
+    """Only shapes the kernel instantiates: head dim 128."""
+    q = match.kwargs.get("query")
+    meta = getattr(q, "meta", {}).get("val") if q is not None else None
+    return meta is not None and meta.dim() == 4 and meta.shape[-1] == 128
+
+
+def _get_sfdp_patterns():
+    from torch._inductor.fx_passes.fuse_attention import partialize_and_update_signature
+    from torch._inductor.fx_passes.joint_graph import patterns
+    from torch._inductor.pattern_matcher import fwd_only, joint_fwd_bwd
+
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    g_inp = functools.partial(torch.empty, (2, 4, 8, 16), device=device, requires_grad=True)
+    c_inp = functools.partial(torch.tensor, 2.0, device=device)
+    workaround = {"dropout_p": 0.113377}
+    for dtype in [torch.float]:
+        g = functools.partial(g_inp, dtype=dtype)
+        c = functools.partial(c_inp, dtype=dtype)
+        pattern, replacement = _b200_fusion_attention_graph_pattern_1, _b200_fusion_attention_graph_replacement_1
+        args = [g(), g(), g(), c()]
+        name = pattern.__name__
+        # the training (joint) variant is registered only when a backward kernel exists;
+        # the inference variant drops dropout, exactly as the reference partialises it
+        pattern_i = partialize_and_update_signature(pattern, dropout_p=0.0)
+        replacement_i = partialize_and_update_signature(replacement, dropout_p=0.0)
+        yield name + "_inference", {
+            "search_fn": pattern_i, "replace_fn": replacement_i, "example_inputs": args,
+            "trace_fn": fwd_only, "pass_dicts": patterns, "scalar_workaround": {},
+            "extra_check": _pattern_extra_check,
+        }
+
+
+_fx_pass_registered = False
+
+
+def register_fx_pass():
+    """Register the search pattern into ``joint_graph.patterns`` (``:196-230``)."""
+    global _fx_pass_registered
+    if _fx_pass_registered:
+        return
+    from torch._inductor.pattern_matcher import register_replacement
+
+    for _key, kwargs in _get_sfdp_patterns():
+        register_replacement(**kwargs)
+    _fx_pass_registered = True
+
+
+# ---------------------------------------------------------------------------------------
+# Device graph pass: aten SDPA kernels -> b200_sdpa
+# ---------------------------------------------------------------------------------------
+from torch._inductor.custom_graph_pass import CustomGraphModulePass, get_hash_for_files  # noqa: E402
+
+aten = torch.ops.aten
+
+
+class B200AttentionPass(CustomGraphModulePass):
+    """Rewrites ``aten._scaled_dot_product_{flash,efficient,cudnn}_attention`` nodes whose
+    only used output is the attention result (optionally the log-sum-exp) into
+    ``b200_graph.b200_sdpa`` when the kernel supports the case: fp16 / bf16, head dim 128,
+    no dropout, no additive bias, causal or no mask."""
+
+    def __call__(self, gm: torch.fx.GraphModule) -> None:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if node.op != "call_function":
+                continue
+            spec = self._match(node)
+            if spec is None:
+                continue
+            q, k, v, scale, causal = spec
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_function(torch.ops.b200_graph.b200_sdpa.default, (q, k, v, scale, causal))
+            import operator
+
+            ok = True
+            for user in list(node.users):
+                if user.op == "call_function" and user.target is operator.getitem and user.args[1] in (0, 1):
+                    continue
+                if len(user.users) == 0:
+                    continue
+                ok = False
+            if not ok:
+                gm.graph.erase_node(new)
+                continue
+            qv = q.meta.get("val")
+            new.meta["val"] = (torch.empty_like(qv), qv.new_empty(qv.shape[:3], dtype=torch.float32))
+            for user in list(node.users):
+                if user.target is operator.getitem and user.args[1] in (0, 1):
+                    with gm.graph.inserting_before(user):
+                        item = gm.graph.call_function(operator.getitem, (new, user.args[1]))
+                    item.meta.update(user.meta)
+                    user.replace_all_uses_with(item)
+                gm.graph.erase_node(user)
+            gm.graph.erase_node(node)
+            changed = True
+        if changed:
+            gm.graph.lint()
+            gm.recompile()
+
+    @staticmethod
+    def _match(node):
+        t = node.target
+        flash = getattr(aten._scaled_dot_product_flash_attention, "default", None)
+        eff = getattr(aten._scaled_dot_product_efficient_attention, "default", None)
+        cudnn = getattr(getattr(aten, "_scaled_dot_product_cudnn_attention", None), "default", None)
+        kw = dict(node.kwargs)
+        if t is flash:
+            q, k, v = node.args[:3]
+            dropout = node.args[3] if len(node.args) > 3 else kw.get("dropout_p", 0.0)
+            causal = node.args[4] if len(node.args) > 4 else kw.get("is_causal", False)
+            bias = None
+        elif t is eff or (cudnn is not None and t is cudnn):
+            q, k, v = node.args[:3]
+            bias = node.args[3] if len(node.args) > 3 else kw.get("attn_bias")
+            dropout = node.args[5] if len(node.args) > 5 else kw.get("dropout_p", 0.0)
+            causal = node.args[6] if len(node.args) > 6 else kw.get("is_causal", False)
+        else:
+            return None
+        if bias is not None or dropout not in (0, 0.0):
+            return None
+        qv = q.meta.get("val") if hasattr(q, "meta") else None
+        kv = k.meta.get("val") if hasattr(k, "meta") else None
+        if qv is None or kv is None or qv.dim() != 4 or qv.shape[-1] != 128:
+            return None
+        if qv.dtype not in (torch.float16, torch.bfloat16) or qv.device.type != "cuda":
+            return None
+        if causal and kv.shape[2] < qv.shape[2]:
+            return None
+        scale = kw.get("scale")
+        if scale is None:
+            scale = 1.0 / (qv.shape[-1] ** 0.5)
+        return q, k, v, float(scale), bool(causal)
+
+    def uuid(self):
+        return get_hash_for_files((__file__,))

@@ -1,0 +1,87 @@
+"""Lowering policy of the B200 backend.
+
+Surface kept from ``inductor_x/lowering.py``: ``make_reduction`` (tags every realised
+reduction with the axes it keeps / reduces, ``:16-45``), ``_init_set`` (``:150-171``) and
+``_register_b200_inductor_fallbacks`` (the reference's ``_register_npu_inductor_fallbacks``,
+``:173-339``).
+
+What changed underneath.  The reference whitelists ~50 aten ops (``GENERATE_LIST``,
+``:80-148``) and turns *everything else* into an extern call, so e.g. ``gelu``, ``sigmoid``,
+``pow``, ``sin/cos`` and ``index_select`` break fusion.  Here the templates instantiate any
+pointwise / reduction / indexing body, so the policy is inverted: only the op families no
+template exists for (scans, sorts, random numbers, scatter-with-atomics) are forced to
+extern kernels.  The reference's special lowerings are not carried over where they encode
+bugs or NPU workarounds: ``sum_`` always returning fp32 (``:204-215``), the hard-coded
+``[32768, 2]`` fallback (``:211-212``), ``embedding`` ignoring ``padding_idx``
+(``:327-330``).  fp32 accumulation for half inputs and the two-pass variance
+(``var_mean_helper_``, ``:270-325``) are what stock Inductor already does for a backend
+without tuple reductions, which is how ``B200Scheduling`` declares itself.
+"""
+from __future__ import annotations
+
+import torch
+from torch._inductor import ir, lowering
+from torch._inductor.lowering import (_make_reduction_inner, _validate_reduction_axis, fallbacks,
+                                      lowerings, make_fallback)
+
+aten = torch.ops.aten
+prims = torch.ops.prims
+
+# op families without a B200 template: they stay extern (ATen) kernels
+FALLBACK_LIST = [
+    aten.cumsum, aten.cumprod, aten.cummax, aten.cummin, aten.logcumsumexp,
+    aten.sort, aten.topk, aten.scatter_add, aten.scatter_reduce, aten.index_put,
+    aten.index_add, aten.bernoulli, aten.rand, aten.randn, aten.randint, aten.randperm,
+    aten.native_dropout, aten.multinomial, aten.bucketize, aten.searchsorted, aten.histc,
+]
+
+
+def make_reduction(reduction_type: str, override_return_dtype=None):
+    """``Reduction.create`` wrapper that records which axes a reduction keeps and reduces
+    on the IR node (``kept_idx`` / ``reduced_idx``) and realises it, as
+    ``inductor_x/lowering.py:16-45`` does; the kernel emitter reads the tags to tell inner
+    from outer reductions."""
+
+    def inner(x, axis=None, keepdims=False, *, dtype=None):
+        kwargs = _make_reduction_inner(x, axis=axis, keepdims=keepdims, dtype=dtype,
+                                       override_return_dtype=override_return_dtype)
+        result = ir.Reduction.create(reduction_type=reduction_type, input_node=x, **kwargs)
+        data = getattr(getattr(result, "data", None), "data", None)
+        if isinstance(data, ir.Reduction):
+            size = x.get_size()
+            axes = set(_validate_reduction_axis(x, axis))
+            data.kept_idx = [i for i in range(len(size)) if i not in axes]
+            data.reduced_idx = [i for i in range(len(size)) if i in axes]
+            result.realize()
+        return result
+
+    return inner
+
+
+def _init_set(input_list, output_set):
+    """Expand OpOverloadPackets into their overloads (``inductor_x/lowering.py:150-171``)."""
+    for fn in input_list:
+        output_set.add(fn)
+        if isinstance(fn, torch._ops.OpOverloadPacket):
+            for overload in fn.overloads():
+                other = getattr(fn, overload)
+                output_set.add(other)
+
+
+def _register_b200_inductor_fallbacks():
+    """Force the op families in ``FALLBACK_LIST`` to extern kernels.  Returns the overloads
+    that were switched."""
+    targets = set()
+    _init_set(FALLBACK_LIST, targets)
+    switched = []
+    for op in targets:
+        if isinstance(op, torch._ops.OpOverloadPacket):
+            continue
+        if op in lowerings and op not in fallbacks:
+            try:
+                del lowerings[op]
+                make_fallback(op, warn=False)
+                switched.append(op)
+            except Exception:
+                pass
+    return switched

@@ -1,0 +1,148 @@
+"""GPU tests of the torch.compile path: graphs compiled through the B200 backend (template
+instantiation, no Triton) against eager PyTorch on the same inputs - the discipline of the
+reference's own tests (test/npu_indexing/reduction_test.py:28-30, permute_test.py:24-29),
+with the tolerances of this build: rel 1e-5 fp32 reductions, 2e-2 half, bit-exact indices."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import inductor_x_b200  # noqa: F401  (registers the backend for "cuda")
+from oracle import graphs, inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def compile_and_code(fn, *args):
+    from torch._inductor.utils import run_and_get_code
+
+    torch._dynamo.reset()
+    out, code = run_and_get_code(torch.compile(fn), *args)
+    text = "\n".join(code)
+    assert "triton" not in text.split("async_compile.wait")[0].lower().replace("triton_helpers", "") or \
+        "ixb_load_kernel" in text
+    return out, text
+
+
+def test_c1_one_fused_kernel(cuda):
+    d = inputs.c1(512, 1024, seed=3)
+    x, w, b = (d[k].to(cuda) for k in ("x", "w", "b"))
+    out, code = compile_and_code(lambda x, w, b: F.gelu(x * w + b).sum(-1), x, w, b)
+    assert code.count("ixb_load_kernel('''") == 1  # the reference needs three kernels here
+    assert graphs.max_rel_err(out.cpu(), graphs.affine_gelu_rowsum(d["x"].double(), d["w"].double(), d["b"].double())) <= 1e-5
+
+
+def test_c2_one_fused_kernel(cuda):
+    d = inputs.c2(256, 4096, seed=4)
+    x, g, ga, be = (d[k].to(cuda) for k in ("x", "g", "gamma", "beta"))
+    fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5)
+    out, code = compile_and_code(fn, x, g, ga, be)
+    assert code.count("ixb_load_kernel('''") == 1
+    exp = graphs.softmax_layernorm(**d, compute=torch.float64, round_output=False)
+    assert graphs.max_rel_err(out.cpu(), exp) <= 2e-2
+
+
+@pytest.mark.parametrize("shape", [(8, 32, 512, 64), (8, 8, 512, 128), (2053, 1023), (513, 64), (3, 7, 9)])
+def test_pointwise_shapes(cuda, shape):
+    g = torch.Generator().manual_seed(sum(shape))
+    a = torch.randn(*shape, generator=g).to(cuda)
+    b = torch.randn(*shape, generator=g).to(cuda)
+    fn = lambda a, b: torch.sigmoid(a) * b + torch.relu(a - b) * 0.5
+    out, _ = compile_and_code(fn, a, b)
+    torch.testing.assert_close(out, fn(a, b), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dim", [((8, 16, 512, 64), -1), ((8, 16, 512, 64), 2), ((8, 16, 512, 64), 1),
+                                       ((8, 16, 512, 64), 0), ((2053, 1023), -1), ((64, 1000), 1),
+                                       ((37, 4096), 1)])
+def test_sum_mean_dims(cuda, dtype, shape, dim):
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g).to(dtype).to(cuda)
+    for op in (torch.sum, torch.mean, torch.amax):
+        out, _ = compile_and_code(lambda t: op(t, dim), x)
+        exp = op(x.double(), dim)
+        tol = 2e-5 if dtype == torch.float32 else 2e-2
+        floor = float(exp.abs().mean()) or 1.0
+        assert graphs.max_rel_err(out.cpu(), exp.cpu(), floor=floor) <= tol
+
+
+@pytest.mark.parametrize("perm", [(0, 2, 1, 3), (3, 2, 1, 0), (0, 1, 3, 2), (1, 0, 2, 3)])
+def test_permute_pointwise(cuda, perm):
+    x = torch.randn(8, 8, 64, 128, generator=torch.Generator().manual_seed(1)).to(cuda)
+    fn = lambda t: (t.permute(*perm) + 1.0).contiguous()
+    out, _ = compile_and_code(fn, x)
+    assert torch.equal(out, fn(x))
+
+
+def test_c3a_permuted_reductions(cuda):
+    x = inputs.c3a((8, 16, 64, 64), seed=2)["x"].to(cuda)
+    amax, _ = compile_and_code(lambda t: t.permute(0, 2, 1, 3).amax(1), x)
+    assert torch.equal(amax, x.permute(0, 2, 1, 3).amax(1))
+    ssum, _ = compile_and_code(lambda t: t.permute(0, 2, 1, 3).sum(3), x)
+    assert graphs.max_rel_err(ssum.cpu(), graphs.permuted_sum(x.cpu(), torch.float64)) <= 2e-2
+
+
+def test_var_mean_and_argmax(cuda):
+    x = torch.randn(64, 1000, generator=torch.Generator().manual_seed(5)).to(cuda)
+    (var, mean), _ = compile_and_code(lambda t: torch.var_mean(t, -1), x)
+    ev, em = torch.var_mean(x.double(), -1)
+    assert graphs.max_rel_err(var.cpu(), ev.cpu()) <= 1e-5
+    assert graphs.max_rel_err(mean.cpu(), em.cpu(), floor=0.05) <= 1e-5
+    idx, _ = compile_and_code(lambda t: torch.argmax(t, -1), x)
+    assert torch.equal(idx, torch.argmax(x, -1))
+
+
+def test_index_select_and_embedding(cuda):
+    d = inputs.c3b(4096, 128, 2048, seed=6)
+    table, idx = d["table"].to(cuda), d["idx"].to(cuda)
+    out, code = compile_and_code(lambda t, i: t.index_select(0, i) * 1, table, idx)
+    assert "ixb_load_kernel" in code
+    assert torch.equal(out, table.index_select(0, idx))
+
+
+def test_rmsnorm_swiglu_rope(cuda):
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(64, 4096, generator=g).bfloat16().to(cuda)
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).bfloat16().to(cuda)
+    rms = lambda x, w: (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(x.dtype) * w
+    out, code = compile_and_code(rms, x, w)
+    assert code.count("ixb_load_kernel('''") == 1
+    assert graphs.max_rel_err(out.cpu(), graphs.rmsnorm(x.cpu(), w.cpu(), 1e-6, torch.float64)) <= 2e-2
+    up = torch.randn(64, 4096, generator=g).bfloat16().to(cuda)
+    out, _ = compile_and_code(lambda a, b: F.silu(a) * b, x, up)
+    assert graphs.max_rel_err(out.cpu(), graphs.swiglu(x.cpu(), up.cpu(), torch.float64)) <= 2e-2
+    q = torch.randn(2, 4, 64, 128, generator=g).bfloat16().to(cuda)
+    cos, sin = (t.to(cuda) for t in inputs.rope_tables(64, 128))
+
+    def rope(q, cos, sin):
+        d = q.shape[-1] // 2
+        rot = torch.cat([-q[..., d:], q[..., :d]], -1)
+        return (q.float() * cos + rot.float() * sin).to(q.dtype)
+
+    out, _ = compile_and_code(rope, q, cos, sin)
+    assert graphs.max_rel_err(out.cpu(), graphs.rope(q.cpu(), cos.cpu(), sin.cpu(), torch.float64)) <= 2e-2
+
+
+def test_sdpa_is_retargeted_to_the_tcgen05_kernel(cuda):
+    d = inputs.c4(2, 4, 512, 128, seed=9)
+    q, k, v = (d[n].to(cuda) for n in "qkv")
+    fn = lambda q, k, v: F.scaled_dot_product_attention(q, k, v, is_causal=True)
+    out, code = compile_and_code(fn, q, k, v)
+    assert "b200_sdpa" in code
+    exp, _ = graphs.attention(d["q"], d["k"], d["v"], d["scale"], causal=True)
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= 2e-2
+
+
+def test_reference_attention_pattern_is_matched(cuda):
+    p = inputs.c4_pattern(2, 128, 4, 128, seed=4)
+    q, k, v = (p[n].to(cuda) for n in ("query", "key", "value"))
+    inv = p["inv_scale_factor"]
+
+    def pattern(query, key, value):
+        qq, kk, vv = (t.permute(0, 2, 1, 3) for t in (query, key, value))
+        return torch.matmul(qq, kk.transpose(-2, -1)).div(inv).softmax(dim=-1).matmul(vv)
+
+    out, code = compile_and_code(pattern, q, k, v)
+    assert "b200_fa" in code
+    exp = graphs.attention_pattern(p["query"], p["key"], p["value"], inv)
+    assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= 2e-2
