@@ -227,6 +227,10 @@ class B200Kernel(SIMDKernel):
             return self.cse.reduction_cache[key]
         if reduction_type == "welford_reduce":
             result = self.welford_reduce_fallback(dtype, value)
+        elif reduction_type == "online_softmax_reduce":
+            # (row max, sum of exp(value - max)): the row is in registers, so the two-pass
+            # form costs no extra memory traffic
+            result = self.prepare_softmax_twopass_fallback(dtype, value)
         elif reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
             result = self.cse.generate(self.compute, f"c.template reduce_arg<{is_max}>({value})",

@@ -150,8 +150,10 @@ class B200Overrides(OpOverrides):
         with V.kernel.mask_loads(mask, other) as new_mask:
             result = body()
         if isinstance(other, (int, float, bool)):
-            other = constant_literal(other, result.dtype if hasattr(result, "dtype") and result.dtype else torch.float32)
-        return ops.where(new_mask, result, other)
+            dtype = getattr(result, "dtype", None) or torch.float32
+            other = V.ops.constant(other, dtype)
+        # the raw handler (not the OpsValue wrapper): callers read .dtype of the result
+        return V.ops.where(new_mask, result, other)
 
     @staticmethod
     def bitwise_and(a, b):

@@ -86,8 +86,10 @@ def _run_kernel(q, k, v, scale: float, causal: bool):
     from . import ops
 
     dt = q.dtype
-    if dt == torch.float32:  # the reference traces its pattern in fp32 only (:174)
-        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    if dt == torch.float32:
+        # the reference traces its pattern in fp32 only (:174); the tensor-core kernel
+        # takes 16-bit operands, and fp16 keeps three more mantissa bits than bf16
+        q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
     if q.stride(-1) != 1:
         q = q.contiguous()
     if k.stride(-1) != 1:

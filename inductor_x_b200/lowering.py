@@ -50,8 +50,9 @@ def make_reduction(reduction_type: str, override_return_dtype=None):
         if isinstance(data, ir.Reduction):
             size = x.get_size()
             axes = set(_validate_reduction_axis(x, axis))
-            data.kept_idx = [i for i in range(len(size)) if i not in axes]
-            data.reduced_idx = [i for i in range(len(size)) if i in axes]
+            # IR nodes are frozen dataclasses: the tags are set past the freeze
+            object.__setattr__(data, "kept_idx", [i for i in range(len(size)) if i not in axes])
+            object.__setattr__(data, "reduced_idx", [i for i in range(len(size)) if i in axes])
             result.realize()
         return result
 
