@@ -1,0 +1,126 @@
+"""CPU tests of the template instantiator's host logic: graphs are compiled through the
+backend registered for the *cpu* device in dry-run mode, so the generated CUDA source is
+produced and cross-compiled with nvcc for sm_100a but never launched.  What is checked is
+classification (which template, how many kernels), the index analysis and the launch
+chooser - not numerics, which need a GPU (tests/test_compile_gpu.py)."""
+import os
+import re
+import shutil
+
+import pytest
+import sympy
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.skipif(shutil.which("nvcc") is None, reason="nvcc not available")
+
+
+@pytest.fixture(scope="module")
+def dry_backend(tmp_path_factory):
+    os.environ["IXB_CACHE_DIR"] = str(tmp_path_factory.mktemp("ixbcache"))
+    import inductor_x_b200
+    from inductor_x_b200 import config
+    from inductor_x_b200.codegen import B200Scheduling, B200WrapperCodeGen
+    from torch._inductor.codegen.common import (get_scheduling_for_device, get_wrapper_codegen_for_device,
+                                                register_backend_for_device)
+
+    config.dry_run = True
+    config.cache_dir = os.environ["IXB_CACHE_DIR"]
+    torch._inductor.config.fx_graph_cache = False
+    from torch._inductor.codegen.common import init_backend_registration
+
+    init_backend_registration()
+    old = (get_scheduling_for_device("cpu"), get_wrapper_codegen_for_device("cpu"))
+    register_backend_for_device("cpu", B200Scheduling, B200WrapperCodeGen)
+    yield
+    register_backend_for_device("cpu", *old)
+    config.dry_run = False
+
+
+def generated(fn, *args):
+    from torch._inductor.utils import run_and_get_code
+
+    torch._dynamo.reset()
+    _, code = run_and_get_code(torch.compile(fn), *args)
+    return "\n".join(code)
+
+
+def test_c1_graph_is_one_row_kernel(dry_backend):
+    code = generated(lambda x, w, b: F.gelu(x * w + b).sum(-1), torch.randn(64, 1024), torch.randn(1024),
+                     torch.randn(1024))
+    assert code.count("ixb_load_kernel('''") == 1
+    assert "launch_row_gen<Body, float, 64, 4, 4>" in code          # 1024 fp32 = 256 vectors
+    assert code.count("c.load_row(") == 3 and "reduce<ixb::SumOp>" in code
+    assert "triton" not in code.split("ixb_load_kernel")[1]
+
+
+def test_c2_chain_is_one_row_kernel_with_four_reductions(dry_backend):
+    fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5)
+    code = generated(fn, torch.randn(32, 4096).bfloat16(), *(torch.randn(4096).bfloat16() for _ in range(3)))
+    assert code.count("ixb_load_kernel('''") == 1
+    assert "launch_row_gen<Body, ixb::bf16, 128, 2, 4>" in code      # 4096 bf16 = 512 vectors
+    assert len(re.findall(r"c\.template reduce<", code)) == 4
+    assert "c.store_row(" in code
+
+
+def test_pointwise_uses_128bit_access_when_contiguous(dry_backend):
+    code = generated(lambda a, b: F.silu(a) * b, torch.randn(8, 1000).bfloat16(), torch.randn(8, 1000).bfloat16())
+    assert "launch_pointwise<Body>" in code and "kVec = 8" in code
+    assert code.count("ldvec<ixb::bf16, kVec>") == 2 and "stvec<ixb::bf16, kVec>" in code
+    assert "gather(" not in code
+
+
+def test_permuted_store_falls_back_to_scatter_or_gather(dry_backend):
+    code = generated(lambda t: (t.permute(0, 2, 1) + 1).contiguous(), torch.randn(4, 16, 24))
+    assert "launch_pointwise<Body>" in code
+    assert "gather(" in code or "scatter(" in code
+
+
+def test_index_analysis():
+    from inductor_x_b200.codegen import ir
+    from torch.utils._sympy.functions import FloorDiv, ModularIndexing
+
+    x, r = sympy.Symbol("xindex", integer=True, nonnegative=True), sympy.Symbol("r0_index", integer=True, nonnegative=True)
+    # flat contiguous and row-broadcast accesses are vector-contiguous, a transpose is not
+    assert ir.is_vector_contiguous(x, x, 8, 1 << 20)
+    assert ir.is_vector_contiguous(ModularIndexing(x, 1, 4096), x, 8, 1 << 20)
+    assert ir.is_vector_contiguous(ModularIndexing(x, 1, 4096) + 4096 * FloorDiv(x, 4096), x, 8, 1 << 20)
+    assert not ir.is_vector_contiguous(64 * ModularIndexing(x, 1, 128) + FloorDiv(x, 128), x, 8, 1 << 13)
+    assert not ir.is_vector_contiguous(ModularIndexing(x, 1, 1023), x, 8, 1023 * 8)
+    # reduction strides: inner (1), outer (constant > 1), flattened multi-axis (None)
+    assert ir.reduction_stride(r + 4096 * x, x, r, 100, 4096) == 1
+    assert ir.reduction_stride(ModularIndexing(x, 1, 64) + 64 * r + 16384 * FloorDiv(x, 64), x, r, 8192, 256) == 64
+    assert ir.reduction_stride(x, x, r, 10, 10) == 0
+    assert ir.reduction_stride(ModularIndexing(r, 1, 8) * 100 + FloorDiv(r, 8), x, r, 4, 64) is None
+
+
+def test_launch_chooser():
+    from inductor_x_b200.codegen import split_tiling as st
+
+    c = st.choose_row_config(4096, torch.bfloat16)
+    assert (c.team, c.vpt, c.vec, c.teams) == (128, 4, 8, 2) and c.capacity >= 4096
+    c = st.choose_row_config(1000, torch.float32)
+    assert c.capacity >= 1000 and c.vec == 4
+    assert st.choose_row_config(1 << 20, torch.float32) is None
+    assert st.choose_pointwise_vec([torch.float32, torch.bfloat16]) == 8
+    assert st.choose_pointwise_vec([torch.float32]) == 4
+    assert st.should_use_persistent_reduction(4096, torch.bfloat16)
+    assert not st.should_use_persistent_reduction(sympy.Symbol("s0"), torch.float32)
+
+
+def test_registration_surface():
+    import inductor_x_b200
+    from inductor_x_b200 import decomposition, fusion_attention_graph, lowering
+    from torch._inductor.codegen.common import get_scheduling_for_device
+
+    assert get_scheduling_for_device("cuda").__name__ == "B200Scheduling"
+    assert callable(inductor_x_b200.get_current_raw_stream)
+    assert all(present for _, present in decomposition._register_b200_inductor_decompositions())
+    s = set()
+    lowering._init_set([torch.ops.aten.cumsum], s)
+    assert torch.ops.aten.cumsum.default in s
+    assert hasattr(torch.ops.b200_graph, "b200_fa") and hasattr(torch.ops.b200_graph, "b200_fa_backward")
+    # Meta implementation mirrors the reference's output shapes (softmax stats [B, N, S, 8])
+    q = torch.empty(2, 4, 16, 128, device="meta", dtype=torch.bfloat16)
+    out = torch.ops.b200_graph.b200_fa(q, q, q, 4, "BNSD")
+    assert out[0].shape == q.shape and out[1].shape == (2, 4, 16, 8) and len(out) == 7
