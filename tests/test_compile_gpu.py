@@ -146,3 +146,21 @@ def test_reference_attention_pattern_is_matched(cuda):
     assert "b200_fa" in code
     exp = graphs.attention_pattern(p["query"], p["key"], p["value"], inv)
     assert graphs.max_rel_err(out.cpu(), exp, dim=-1) <= 2e-2
+
+
+def test_llama_decoder_layer_compiles_to_templates(cuda):
+    """Configuration 5 at reduced width: hidden 512, 4 heads of 128, FFN 1376, 2 x 256 tokens."""
+    from inductor_x_b200.llama_layer import decoder_layer
+
+    w = inputs.c5_weights(hidden=512, heads=4, ffn=1376, seed=0)
+    x = inputs.c5_input(2, 256, 512, seed=1)
+    cos, sin = inputs.rope_tables(256, 128)
+    wd = {k: v.to(cuda) for k, v in w.items()}
+    fn = lambda x, cos, sin: decoder_layer(x, wd, cos, sin, heads=4)
+    out, code = compile_and_code(fn, x.to(cuda), cos.to(cuda), sin.to(cuda))
+    assert "b200_sdpa" in code and "ixb_load_kernel" in code
+    assert "triton_" not in code.replace("triton_helpers", "")
+    exp = graphs.llama_layer(x, w, heads=4, compute=torch.float64)
+    assert graphs.max_rel_err(out.cpu(), exp) <= 2e-2
+    eager = fn(x.to(cuda), cos.to(cuda), sin.to(cuda))
+    assert graphs.max_rel_err(out.cpu(), eager.cpu()) <= 2e-2
