@@ -526,6 +526,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the Python enqueue loop instead of a CUDA graph")
     ap.add_argument("--c4-batch", type=int, default=0,
                     help="override the attention batch (profiling captures on a smaller case)")
     args = ap.parse_args()
@@ -570,24 +571,55 @@ def main():
         wl.step(i)
     barrier()
 
-    # ---- timed region: exactly K steps, CUDA events on the launching (current) stream
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    # ---- timed region: exactly K steps, CUDA events on the launching stream.  The K launches
+    # are captured into one CUDA graph and replayed, so a kernel of a few microseconds is
+    # timed back to back on the device instead of at the pace Python can enqueue it
+    # (--no-graph times the plain enqueue loop).
+    use_graph = not args.no_graph and not isinstance(wl, LlamaLayer)
+    graph = None
     launches = 0
+    if use_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(args.steps):
+                        launches += wl.step(i)
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()  # one untimed replay
+            barrier()
+        except Exception as e:  # capture not possible: time the enqueue loop instead
+            print(f"graph capture failed ({type(e).__name__}: {e}); timing the enqueue loop", file=sys.stderr)
+            graph, launches = None, 0
+            torch.cuda.synchronize()
     t_wall0 = time.perf_counter()
     whole0 = torch.cuda.Event(enable_timing=True)
     whole1 = torch.cuda.Event(enable_timing=True)
-    whole0.record()
-    for i in range(args.steps):
-        starts[i].record()
-        launches += wl.step(i)
-        ends[i].record()
-    whole1.record()
-    barrier()
-    t_wall1 = time.perf_counter()
-    total_ms = whole0.elapsed_time(whole1)
-    kernel_ms = sorted(s.elapsed_time(e) for s, e in zip(starts, ends))
-    avg_kernel_ms = sum(kernel_ms) / len(kernel_ms)
+    if graph is not None:
+        whole0.record()
+        graph.replay()
+        whole1.record()
+        barrier()
+        t_wall1 = time.perf_counter()
+        total_ms = whole0.elapsed_time(whole1)
+        avg_kernel_ms = total_ms / args.steps
+        kernel_ms = [avg_kernel_ms]
+    else:
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        whole0.record()
+        for i in range(args.steps):
+            starts[i].record()
+            launches += wl.step(i)
+            ends[i].record()
+        whole1.record()
+        barrier()
+        t_wall1 = time.perf_counter()
+        total_ms = whole0.elapsed_time(whole1)
+        kernel_ms = sorted(s.elapsed_time(e) for s, e in zip(starts, ends))
+        avg_kernel_ms = sum(kernel_ms) / len(kernel_ms)
     if world > 1:
         t = torch.tensor([total_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -653,7 +685,8 @@ def main():
             "config": {"workload": wl.name, "algorithmic_bytes_per_step": nbytes,
                        "l2": "working set per step exceeds the 126 MB L2 and steps rotate over "
                              f"{len(getattr(wl, 'xs', getattr(wl, 'idxs', [0])))} distinct buffer sets",
-                       "sharding": f"rows split over {world} GPU(s), no collective"},
+                       "sharding": f"rows split over {world} GPU(s), no collective",
+                       "timed_region": "one CUDA graph of the K launches" if graph is not None else "enqueue loop"},
             "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                          "unit": unit, "frac": achieved / peak, "traffic": traffic,
                          "peak_source": peaks["source"], "kernel_ms_avg": avg_kernel_ms,

@@ -60,7 +60,7 @@ struct AffineGeluRowSum {
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (c.ok(i, j)) acc += gelu_erf(fmaf(x[j], w[j], b[j]));
+          if (c.ok(i, j)) acc += gelu_erf_fast(fmaf(x[j], w[j], b[j]));
       }
       acc = c.template reduce<SumOp>(acc);
       if (c.lane == 0) p.out[r] = acc;
