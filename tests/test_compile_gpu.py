@@ -164,3 +164,75 @@ def test_llama_decoder_layer_compiles_to_templates(cuda):
     assert graphs.max_rel_err(out.cpu(), exp) <= 2e-2
     eager = fn(x.to(cuda), cos.to(cuda), sin.to(cuda))
     assert graphs.max_rel_err(out.cpu(), eager.cpu()) <= 2e-2
+
+
+# ---- graphs modelled on the reference's own compile-vs-eager tests (test/npu_indexing) ----
+@pytest.mark.parametrize("dim", [0, 1, 2, 3])
+@pytest.mark.parametrize("perm", [(0, 1, 3, 2), (0, 2, 1, 3), (2, 1, 0, 3), (3, 1, 2, 0), (1, 0, 2, 3)])
+def test_reduction_broadcast_permute(cuda, dim, perm):
+    """sum over one dim, broadcast back, permute (reduction_broadcast_permute_test.py:20-33)."""
+    x = torch.randn(8, 8, 64, 32, generator=torch.Generator().manual_seed(dim)).to(cuda)
+    fn = lambda t: (t - t.sum(dim, keepdim=True)).permute(*perm).contiguous()
+    out, _ = compile_and_code(fn, x)
+    torch.testing.assert_close(out, fn(x), rtol=1e-4, atol=1e-4)
+
+
+def test_rearrange_b_n_s_d_to_s_b_nd(cuda):
+    """'b n s d -> s b (n d)' (permute_reshape_test.py:9-31)."""
+    x = torch.randn(4, 8, 96, 64, generator=torch.Generator().manual_seed(2)).to(cuda)
+    fn = lambda t: (t * 2.0).permute(2, 0, 1, 3).reshape(96, 4, 512)
+    out, _ = compile_and_code(fn, x)
+    assert torch.equal(out, fn(x))
+
+
+@pytest.mark.parametrize("dims", [(0,), (1,), (2,), (0, 2), (1, 2), (0, 1, 2)])
+def test_var_mean_axis_sets(cuda, dims):
+    """var_mean over several axis sets (var_mean_test.py:28-36)."""
+    x = torch.randn(16, 24, 40, generator=torch.Generator().manual_seed(len(dims))).to(cuda)
+    (var, mean), _ = compile_and_code(lambda t: torch.var_mean(t, dims), x)
+    ev, em = torch.var_mean(x.double(), dims)
+    torch.testing.assert_close(var.double(), ev, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(mean.double(), em, rtol=1e-4, atol=1e-5)
+
+
+def test_repeat_and_unaligned_argmax(cuda):
+    """repeat (repeat_test.py:28-31) and argmax on unaligned shapes (argmax_unalign_test.py:36-55)."""
+    x = torch.randn(3, 513, generator=torch.Generator().manual_seed(9)).to(cuda)
+    out, _ = compile_and_code(lambda t: t.repeat(2, 3) + 1, x)
+    assert torch.equal(out, x.repeat(2, 3) + 1)
+    for shape in [(513, 64), (7, 1023), (129, 300)]:
+        y = torch.randn(*shape, generator=torch.Generator().manual_seed(shape[0])).to(cuda)
+        idx, _ = compile_and_code(lambda t: torch.argmax(t, -1), y)
+        assert torch.equal(idx, torch.argmax(y, -1))
+
+
+def test_mamba_split_permute(cuda):
+    """split + permute + elementwise of the mamba regression graph (mamba_test.py:7-29)."""
+    x = torch.randn(4, 64, 96, generator=torch.Generator().manual_seed(11)).to(cuda)
+
+    def fn(t):
+        a, b, c = torch.split(t, [32, 32, 32], dim=-1)
+        return (F.silu(a) * b + c).permute(0, 2, 1).contiguous()
+
+    out, _ = compile_and_code(fn, x)
+    torch.testing.assert_close(out, fn(x), rtol=1e-5, atol=1e-5)
+
+
+def test_context_parallel_softmax_merge(cuda):
+    """Online-softmax merge of two attention partials, the per-step math of ring attention
+    (attn_cp_test.py:36-59 forward_update)."""
+    g = torch.Generator().manual_seed(13)
+    prev_out, cur_out = (torch.randn(2, 4, 128, 64, generator=g).to(cuda) for _ in range(2))
+    prev_max, cur_max = (torch.randn(2, 4, 128, 1, generator=g).to(cuda) for _ in range(2))
+    prev_sum, cur_sum = (torch.rand(2, 4, 128, 1, generator=g).to(cuda) + 0.5 for _ in range(2))
+
+    def forward_update(po, pm, ps, co, cm, cs):
+        m = torch.maximum(pm, cm)
+        ps2 = ps * torch.exp(pm - m)
+        cs2 = cs * torch.exp(cm - m)
+        s = ps2 + cs2
+        return po * (ps2 / s) + co * (cs2 / s), m, s
+
+    outs, _ = compile_and_code(forward_update, prev_out, prev_max, prev_sum, cur_out, cur_max, cur_sum)
+    for a, e in zip(outs, forward_update(prev_out, prev_max, prev_sum, cur_out, cur_max, cur_sum)):
+        torch.testing.assert_close(a, e, rtol=1e-5, atol=1e-5)
