@@ -58,7 +58,10 @@ class B200Kernel(SIMDKernel):
 
     def __init__(self, tiling, **kwargs: Any) -> None:
         self._row_cfg: Optional[split_tiling.RowConfig] = None
-        self._buffer_dtypes: list = []
+        self._ph: dict = {}
+        self._ph_by_key: dict = {}
+        self.x_indexing = IndentedBuffer()
+        self.r_indexing = IndentedBuffer()
         super().__init__(tiling, **kwargs)
         self.is_row = self.features.is_reduction()
         if self.is_row:
@@ -70,6 +73,7 @@ class B200Kernel(SIMDKernel):
                     f"reduced extent {rnumel} does not fit the persistent row template")
             if any(p.startswith("r") and p != "r0_" for p in self.numels):
                 raise UnsupportedByTemplates("multi-axis reduction tilings")
+            self._outer_vec = split_tiling.choose_pointwise_vec(self._node_dtypes())
         else:
             self.vec = split_tiling.choose_pointwise_vec(self._node_dtypes())
 
@@ -133,19 +137,41 @@ class B200Kernel(SIMDKernel):
 
     def codegen_iteration_ranges_entry(self, entry: IterationRangesEntry) -> None:
         expr = self.rename_indexing(entry.expr)
-        self.indexing_code.writeline(f"const auto {entry.name} = {self.sexpr(expr)};")
+        line = f"const auto {entry.name} = {self.sexpr(expr)};"
+        # reduced-axis variables live inside the reduction loop of the outer mapping
+        (self.r_indexing if entry.is_reduction else self.x_indexing).writeline(line)
 
-    # ------------------------------------------------------------------ masks
-    def _base_mask(self, vector: bool) -> str:
-        if self.is_row:
-            return "rmask" if vector else "(c.lane == 0)"
-        return "xmask"
+    # ------------------------------------------------------------------ two mappings
+    # A reduction group can be laid out in two ways and the choice is only known once the
+    # whole group has been seen:
+    #   row    - the reduced axis is held by a team (xindex scalar, r0_index a vector)
+    #   outer  - threads map along the kept axis (xindex a vector, r0_index the scalar loop
+    #            variable of a loop emitted around everything before the reduction)
+    # Expression text is rank-agnostic (auto + overloads), so only loads, stores and the
+    # reduction itself differ.  Those are emitted as placeholders that carry both texts
+    # and are substituted in codegen_kernel.
+    def _placeholder(self, kind: str, key, row_text: str, outer_text: str, **info) -> str:
+        table = self._ph_by_key
+        if key is not None and key in table:
+            return table[key]
+        tag = f"@{kind}{len(self._ph)}@"
+        self._ph[tag] = dict(kind=kind, row=row_text, outer=outer_text, **info)
+        if key is not None:
+            table[key] = tag
+        return tag
 
-    def _load_mask_expr(self, vector: bool, for_store: bool) -> str:
-        m = self._base_mask(vector) if (for_store or vector or not self.is_row) else "true"
-        if not for_store and self._load_mask is not None:
-            m = f"ixb::gen::op::logical_and({m}, {self._load_mask})"
-        return m
+    def _xr_roots(self):
+        return self._root("x"), self._root("r0_")
+
+    def _outer_x_contiguous(self, exp: sympy.Expr) -> bool:
+        """x-vector contiguity of an access for every value of the reduced index."""
+        xr, rr = self._xr_roots()
+        rn = self._static_numel("r0_")
+        for r in sorted({0, rn - 1, rn // 2}):
+            e = exp.subs({rr.symbol(): r}) if rr is not None else exp
+            if not index_ir.is_vector_contiguous(e, xr.symbol(), self._outer_vec, self._static_numel("x")):
+                return False
+        return True
 
     # ------------------------------------------------------------------ loads
     def load(self, name: str, index: sympy.Expr) -> CSEVariable:
@@ -160,27 +186,39 @@ class B200Kernel(SIMDKernel):
         other = {torch.float32: f"(float)({other})", torch.int64: f"(long long)({other})",
                  torch.bool: f"(bool)({other})"}[val_dtype]
         masked = self._load_mask is not None
+        lm = f"ixb::gen::op::logical_and(@M@, {self._load_mask})" if masked else "@M@"
+        gather = f"{G}gather({var}, {idx}, {lm}, {other})"
 
-        line = None
-        if not indirect and not masked:
-            exp = self._expanded(index)
-            if self.is_row:
-                xr, rr = self._root("x"), self._root("r0_")
-                if self.inside_reduction and rr is not None and rr.symbol() in exp.free_symbols:
-                    stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(),
-                                                       self._static_numel("x"), self._static_numel("r0_"))
-                    if stride == 1:
-                        # row-contiguous: 128-bit loads from the start of this row
-                        line = (f"c.load_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)))")
-            else:
-                xr = self._root("x")
-                if index_ir.is_vector_contiguous(exp, xr.symbol(), self.vec, self._static_numel("x")):
+        if not self.is_row:
+            line = gather.replace("@M@", "xmask")
+            if not indirect and not masked:
+                exp = self._expanded(index)
+                if index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec, self._static_numel("x")):
                     line = f"{G}ldvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid)"
-        if line is None:
-            vector = (not self.is_row) or self._has_reduction_var(index) or indirect
-            mask = self._load_mask_expr(vector, for_store=False)
-            line = f"{G}gather({var}, {idx}, {mask}, {other})"
-        return self.cse.generate(self.compute, line, dtype=val_dtype)
+            return self.cse.generate(self.compute, line, dtype=val_dtype)
+
+        # reduction group: text for both mappings
+        exp = self._expanded(index)
+        xr, rr = self._xr_roots()
+        has_r = rr is not None and rr.symbol() in exp.free_symbols
+        stride = None
+        if not indirect and has_r and self.inside_reduction:
+            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
+                                               self._static_numel("r0_"))
+        vector_row = has_r or indirect
+        row_text = gather.replace("@M@", "rmask" if vector_row else "true")
+        if stride == 1 and not masked:
+            row_text = f"c.load_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)))"
+        outer_text = gather.replace("@M@", "xmask")
+        x_contig = False
+        if not indirect and not masked and xr.symbol() in exp.free_symbols:
+            x_contig = self._outer_x_contiguous(exp)
+            if x_contig:
+                outer_text = f"{G}ldvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid)"
+        tag = self._placeholder("L", (name, idx, str(self._load_mask), other), row_text, outer_text,
+                                stride=stride, has_r=has_r, x_contig=x_contig, indirect=indirect,
+                                in_reduction=self.inside_reduction)
+        return self.cse.generate(self.compute, tag, dtype=val_dtype)
 
     # ------------------------------------------------------------------ stores
     def store(self, name: str, index: sympy.Expr, value: CSEVariable, mode=None) -> None:
@@ -191,33 +229,40 @@ class B200Kernel(SIMDKernel):
         idx = self.index_to_str(index)
         if mode is not None:
             raise UnsupportedByTemplates(f"store mode {mode}")
-        line = None
-        if not self._is_indirect(index):
-            exp = self._expanded(index)
-            if self.is_row:
-                xr, rr = self._root("x"), self._root("r0_")
-                if self.inside_reduction and rr is not None and rr.symbol() in exp.free_symbols:
-                    stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(),
-                                                       self._static_numel("x"), self._static_numel("r0_"))
-                    if stride == 1:
-                        line = (f"c.store_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)), {value});")
-            else:
-                xr = self._root("x")
-                if index_ir.is_vector_contiguous(exp, xr.symbol(), self.vec, self._static_numel("x")):
-                    line = f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid, {value});"
-        if line is None:
-            vector = (not self.is_row) or self._has_reduction_var(index) or self._is_indirect(index)
-            mask = self._base_mask(vector)
-            line = f"{G}scatter({var}, {idx}, {mask}, {value});"
+        indirect = self._is_indirect(index)
+        exp = self._expanded(index)
+        if not self.is_row:
+            line = f"{G}scatter({var}, {idx}, xmask, {value});"
+            if not indirect and index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec,
+                                                              self._static_numel("x")):
+                line = f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid, {value});"
+            self.compute.writeline(DeferredLine(name, line))
+            return
+        xr, rr = self._xr_roots()
+        has_r = rr is not None and rr.symbol() in exp.free_symbols
+        vector_row = has_r or indirect
+        row_text = f"{G}scatter({var}, {idx}, {'rmask' if vector_row else '(c.lane == 0)'}, {value});"
+        if not indirect and has_r and self.inside_reduction:
+            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
+                                               self._static_numel("r0_"))
+            if stride == 1:
+                row_text = f"c.store_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)), {value});"
+        outer_text = f"{G}scatter({var}, {idx}, ixb::gen::op::logical_and(xmask, c.ty == 0), {value});"
+        if not indirect and not has_r and self._outer_x_contiguous(exp):
+            outer_text = (f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), c.ty == 0 ? nvalid : 0, "
+                          f"{value});")
+        tag = self._placeholder("S", None, row_text, outer_text, has_r=has_r,
+                                in_reduction=self.inside_reduction)
         # dropped at print time if the buffer turns out to be internal to the kernel
-        self.compute.writeline(DeferredLine(name, line))
+        self.compute.writeline(DeferredLine(name, tag))
 
     def store_reduction(self, name: str, index: sympy.Expr, value: CSEVariable) -> None:
-        var = self.args.output(name)
-        index = self.prepare_indexing(index)
-        idx = self.index_to_str(index)
-        # one thread of the team writes the per-row result
-        self.compute.writeline(DeferredLine(name, f"{G}scatter({var}, {idx}, (c.lane == 0), {value});"))
+        prior = self.inside_reduction
+        self.inside_reduction = False
+        try:
+            self.store(name, index, value)
+        finally:
+            self.inside_reduction = prior
 
     # ------------------------------------------------------------------ reductions
     def reduction(self, dtype, src_dtype, reduction_type, value):
@@ -233,18 +278,27 @@ class B200Kernel(SIMDKernel):
             result = self.prepare_softmax_twopass_fallback(dtype, value)
         elif reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
-            result = self.cse.generate(self.compute, f"c.template reduce_arg<{is_max}>({value})",
-                                       dtype=torch.int64)
+            tag = self._placeholder("R", None, f"c.template reduce_arg<{is_max}>({value})", "", outer_ok=False)
+            self.compute.writeline(f"@B{tag[2:]}")
+            result = self.cse.generate(self.compute, tag, dtype=torch.int64)
         elif reduction_type == "any":
-            result = self.cse.generate(self.compute, f"c.reduce_any({value})", dtype=torch.bool)
+            tag = self._placeholder("R", None, f"c.reduce_any({value})", "", outer_ok=False)
+            self.compute.writeline(f"@B{tag[2:]}")
+            result = self.cse.generate(self.compute, tag, dtype=torch.bool)
         elif reduction_type in REDUCTION_OPS:
-            text = f"c.template reduce<{REDUCTION_OPS[reduction_type]}>({value})"
-            if src_dtype in INT_DTYPES or src_dtype == torch.bool:
-                # exact up to 2^24; integer reductions beyond that need an integer team exchange
-                text = f"ixb::gen::op::to_int({text})"
-                result = self.cse.generate(self.compute, text, dtype=torch.int64)
-            else:
-                result = self.cse.generate(self.compute, text, dtype=torch.float32)
+            op = REDUCTION_OPS[reduction_type]
+            is_int = src_dtype in INT_DTYPES or src_dtype == torch.bool
+            row_text = f"c.template reduce<{op}>({value})"
+            outer_text = f"c.template combine<{op}>(acc)"
+            if is_int:
+                # exact up to 2^24; integer reductions beyond that need an integer exchange
+                row_text = f"ixb::gen::op::to_int({row_text})"
+                outer_text = f"ixb::gen::op::to_int({outer_text})"
+            tag = self._placeholder("R", None, row_text, outer_text, outer_ok=True, op=op,
+                                    value=str(value), rtype=reduction_type)
+            self.compute.writeline(f"@B{tag[2:]}")  # marks where the reduction loop ends
+            result = self.cse.generate(self.compute, tag,
+                                       dtype=torch.int64 if is_int else torch.float32)
         else:
             raise UnsupportedByTemplates(f"reduction type {reduction_type}")
         self.cse.reduction_cache[key] = result
@@ -288,10 +342,44 @@ class B200Kernel(SIMDKernel):
                 raise UnsupportedByTemplates(f"kernel argument {arg!r}")
         return decls, assigns, call_args
 
+    # ------------------------------------------------------------------ mapping choice
+    def _choose_outer(self, body_text: str) -> bool:
+        """Outer mapping iff the group is one ordinary reduction whose reduced axis is not
+        stride-1 in any load, at least one load is contiguous along the kept axis, nothing
+        r-dependent is stored, and nothing computed inside the reduction loop is used after
+        it except the reduction result."""
+        import re
+
+        reds = [v for v in self._ph.values() if v["kind"] == "R"]
+        if len(reds) != 1 or not reds[0].get("outer_ok"):
+            return False
+        loads = [v for v in self._ph.values() if v["kind"] == "L" and v["has_r"]]
+        if not loads or any(v["indirect"] or v["stride"] in (None, 1) for v in loads):
+            return False
+        if not any(v["x_contig"] for v in loads):
+            return False
+        if any(v["kind"] == "S" and v["has_r"] for v in self._ph.values()):
+            return False
+        marker = next(t for t, v in self._ph.items() if v["kind"] == "R").replace("@R", "@B")
+        head, _, tail = body_text.partition(marker)
+        defined = set(re.findall(r"const auto (tmp\d+) =", head))
+        used_after = set(re.findall(r"\b(tmp\d+)\b", tail))
+        return not (defined & used_after)
+
+    def _substitute(self, text: str, outer: bool) -> str:
+        for tag, v in self._ph.items():
+            text = text.replace(tag, v["outer"] if outer else v["row"])
+        return text
+
     def codegen_kernel(self, name: Optional[str] = None) -> str:
         self.codegen_body()
         decls, assigns, _ = self._kernel_args()
         xnumel = self._static_numel("x")
+        body_text = self.body.getvalue()
+        x_idx, r_idx = self.x_indexing.getvalue(), self.r_indexing.getvalue()
+        outer = self.is_row and self._choose_outer(body_text)
+        self.mapping = "outer" if outer else ("row" if self.is_row else "pointwise")
+
         src = IndentedBuffer()
         src.writeline('#include "ixb/gen.cuh"')
         src.writeline("namespace {")
@@ -300,24 +388,54 @@ class B200Kernel(SIMDKernel):
         with src.indent():
             for d in decls:
                 src.writeline(d)
-            if self.is_row:
-                cfg = self._row_cfg
+            if outer:
+                red_tag, red = next((t, v) for t, v in self._ph.items() if v["kind"] == "R")
+                marker = red_tag.replace("@R", "@B")
+                head, _, tail = body_text.partition(marker)
+                rnumel = self._static_numel("r0_")
+                acc_line = {
+                    "sum": "acc = ixb::gen::op::add(acc, ixb::gen::op::to_float({v}));",
+                    "prod": "acc = ixb::gen::op::mul(acc, ixb::gen::op::to_float({v}));",
+                    "max": "acc = ixb::gen::op::maximum(acc, ixb::gen::op::to_float({v}));",
+                    "min": "acc = ixb::gen::op::minimum(acc, ixb::gen::op::to_float({v}));",
+                }[red["rtype"]].format(v=red["value"])
+                src.writeline(f"static constexpr int kVec = {self._outer_vec};")
+                src.writeline("template <class Ctx>")
+                src.writeline("__device__ __forceinline__ void tile(Ctx& c, const long long xbase, const int nvalid) const {")
+                with src.indent():
+                    src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
+                    src.writeline("const auto xmask = xindex < (xbase + nvalid);")
+                    src.splice(x_idx)
+                    src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
+                    src.writeline("#pragma unroll 4")  # independent loads of four steps in flight
+                    src.writeline(f"for (long long r0_index = c.ty; r0_index < {rnumel}LL; r0_index += Ctx::kTY) {{")
+                    with src.indent():
+                        src.splice(r_idx)
+                        src.splice(self._substitute(head, True))
+                        src.writeline(acc_line)
+                    src.writeline("}")
+                    src.splice(self._substitute(tail, True))
+                src.writeline("}")
+            elif self.is_row:
+                import re
+
                 src.writeline("template <class Ctx>")
                 src.writeline("__device__ __forceinline__ void row(Ctx& c, const long long xindex) const {")
                 with src.indent():
                     src.writeline("const auto r0_index = c.rindex();")
                     src.writeline("const auto rmask = c.rmask();")
-                    src.splice(self.indexing_code)
-                    src.splice(self.body)
+                    src.splice(x_idx)
+                    src.splice(r_idx)
+                    src.splice(re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False)))
                 src.writeline("}")
             else:
                 src.writeline(f"static constexpr int kVec = {self.vec};")
                 src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid) const {")
                 with src.indent():
                     src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
-                    src.writeline(f"const auto xmask = xindex < (xbase + nvalid);")
-                    src.splice(self.indexing_code)
-                    src.splice(self.body)
+                    src.writeline("const auto xmask = xindex < (xbase + nvalid);")
+                    src.splice(x_idx)
+                    src.splice(body_text)
                 src.writeline("}")
         src.writeline("};")
         src.writeline("}  // namespace")
@@ -326,20 +444,22 @@ class B200Kernel(SIMDKernel):
             src.writeline("Body b;")
             for a in assigns:
                 src.writeline(a)
-            if self.is_row:
+            if outer:
+                src.writeline(f"return {G}launch_outer_gen<Body>(b, {xnumel}LL, stream);")
+            elif self.is_row:
                 cfg = self._row_cfg
                 rnumel = self._static_numel("r0_")
-                rt = self.dtype_to_str(self._narrowest_node_dtype())
-                if cfg.vec * {"float": 4, "double": 8}.get(rt, 2) != 16:
-                    rt = {4: "float", 8: "ixb::bf16"}[cfg.vec]
+                rt = {4: "float", 8: "ixb::bf16"}[cfg.vec]
+                narrow = self._narrowest_node_dtype()
+                if cfg.vec == 8 and narrow == torch.float16:
+                    rt = "ixb::f16"
                 src.writeline(f"return {G}launch_row_gen<Body, {rt}, {cfg.team}, {cfg.teams}, {cfg.vpt}>"
                               f"(b, {xnumel}LL, {rnumel}, stream);")
             else:
                 src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream);")
         src.writeline("}")
         text = src.getvalue()
-        family = "row" if self.is_row else "pointwise"
-        return f"ixb_load_kernel('''\n{text}''', family={family!r})"
+        return f"ixb_load_kernel('''\n{text}''', family={self.mapping!r})"
 
     def call_kernel(self, name: str, node: Any = None, deallocate_ws: bool = True) -> None:
         wrapper = V.graph.wrapper_code

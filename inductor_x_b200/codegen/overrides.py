@@ -58,14 +58,14 @@ class IxbExprPrinter(ExprPrinter):
 
     def _print_FloorDiv(self, expr):
         x, d = expr.args
-        return f"{OP}floordiv({self.doprint(x)}, {self.doprint(d)})"
+        return f"{OP}idiv({self.doprint(x)}, {self.doprint(d)})"
 
     def _print_ModularIndexing(self, expr):
         x, d, m = expr.args
         xs = self.doprint(x)
         if d != 1:
-            xs = f"{OP}floordiv({xs}, {self.doprint(d)})"
-        return f"{OP}mod({xs}, {self.doprint(m)})"
+            xs = f"{OP}idiv({xs}, {self.doprint(d)})"
+        return f"{OP}imod({xs}, {self.doprint(m)})"
 
     def _print_Min(self, expr):
         out = self.doprint(expr.args[0])

@@ -52,7 +52,7 @@ class B200Scheduling(SIMDScheduling):
         wrapper = V.graph.wrapper_code
         if src_code in wrapper.src_to_kernel:
             return wrapper.src_to_kernel[src_code]
-        family = "row" if kernel.is_row else "pointwise"
+        family = getattr(kernel, "mapping", "row" if kernel.is_row else "pointwise")
         kernel_name = f"ixb_{family}_{wrapper.next_kernel_suffix()}"
         wrapper.src_to_kernel[src_code] = kernel_name
         origins, detailed = get_kernel_metadata(node_schedule, wrapper)

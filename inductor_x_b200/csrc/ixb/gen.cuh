@@ -7,8 +7,9 @@
 //                                where an operand is contiguous along it)
 //   row_gen_kernel<Body,...>     Body::row(ctx, x): one reduced row held in the registers of
 //                                a team (same work split as row.cuh)
-//   loop_gen_kernel<Body,...>    Body::init / step(x, r) / finish(ctx, x): reductions whose
-//                                reduced axis is not stride-1 or does not fit on chip
+//   outer_gen_kernel<Body,...>   Body::tile(ctx, xbase, nvalid): reductions whose reduced axis
+//                                is not stride-1; threads map along the kept axis and the
+//                                body loops over the reduced index
 //
 // They play the role of the decorators the reference attaches to every emitted kernel,
 // pointwise_npu_index / persistent_reduction_npu_index / reduction_npu_index
@@ -303,6 +304,72 @@ int launch_row_gen(const Body& body, long long rows, int cols, void* stream) {
   long long grid = (long long)sms * resident;
   if (grid > groups) grid = groups;
   kern<<<(unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream>>>(body, rows, cols);
+  return (int)cudaGetLastError();
+}
+
+// ---- outer reduction family -----------------------------------------------------------------
+// The kept (x) axis is stride-1 in memory and the reduced axis is not: threads map along x
+// (kVec consecutive elements each, a warp covers 32 * kVec of them) and the TY thread rows
+// of a CTA split the reduced axis; their partial vectors are folded through shared memory.
+// The generated body carries the loop over the reduced index itself:
+//   Body::tile(ctx, xbase, nvalid)  - for (r = ctx.ty; r < rnumel; r += kTY) {...}, then
+//                                     ctx.combine<Op>(acc), epilogue, stores by ty == 0.
+template <int V, int TX, int TY> struct OuterCtx {
+  static constexpr int kTY = TY;
+  int tx, ty;
+  float* part;  // [TY][TX * V]
+
+  template <int N> static __device__ __forceinline__ vf<N> splat(float v) {
+    vf<N> r;
+#pragma unroll
+    for (int i = 0; i < N; ++i) r.v[i] = v;
+    return r;
+  }
+  // fold the TY partial vectors; every thread row receives the result
+  template <class Op> __device__ __forceinline__ vf<V> combine(const vf<V>& acc) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) part[(ty * TX + tx) * V + i] = acc.v[i];
+    __syncthreads();
+    vf<V> r;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float a = part[tx * V + i];
+#pragma unroll
+      for (int y = 1; y < TY; ++y) a = Op::combine(a, part[(y * TX + tx) * V + i]);
+      r.v[i] = a;
+    }
+    __syncthreads();
+    return r;
+  }
+};
+
+template <class Body, int TX, int TY>
+__global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, const long long xnumel) {
+  constexpr int V = Body::kVec;
+  __shared__ float part[TY * TX * V];
+  OuterCtx<V, TX, TY> c;
+  c.tx = threadIdx.x % TX;
+  c.ty = threadIdx.x / TX;
+  c.part = part;
+  const long long per_cta = (long long)TX * V;
+  const long long ntiles = (xnumel + per_cta - 1) / per_cta;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long xbase = t * per_cta + (long long)c.tx * V;
+    const long long left = xnumel - xbase;
+    body.tile(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
+  }
+}
+template <class Body> int launch_outer_gen(const Body& body, long long xnumel, void* stream) {
+  if (xnumel <= 0) return 0;
+  constexpr int TX = 32, TY = 8;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long per_cta = (long long)TX * Body::kVec;
+  long long grid = (xnumel + per_cta - 1) / per_cta;
+  const long long cap = (long long)sms * 8;
+  if (grid > cap) grid = cap;
+  outer_gen_kernel<Body, TX, TY><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
   return (int)cudaGetLastError();
 }
 

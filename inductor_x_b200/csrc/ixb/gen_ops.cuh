@@ -13,7 +13,9 @@ namespace op {
   template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type NAME(const A& a) { \
     return map1<typename fres<rank<A>::n>::type>([](float x) { return (EXPR); }, a);  \
   }
-IXB_OP_F1(exp, expf(x))
+// exp / sigmoid use the hardware exponential (ex2.approx on a pre-scaled argument), as
+// Inductor's GPU code generation does for these ops
+IXB_OP_F1(exp, __expf(x))
 IXB_OP_F1(exp2, exp2f(x))
 IXB_OP_F1(expm1, expm1f(x))
 IXB_OP_F1(log, logf(x))
@@ -39,7 +41,7 @@ IXB_OP_F1(ceil, ceilf(x))
 IXB_OP_F1(trunc, truncf(x))
 IXB_OP_F1(round, nearbyintf(x))
 IXB_OP_F1(reciprocal, 1.f / x)
-IXB_OP_F1(sigmoid, 1.f / (1.f + expf(-x)))
+IXB_OP_F1(sigmoid, __fdividef(1.f, 1.f + __expf(-x)))
 IXB_OP_F1(to_float, x)
 #undef IXB_OP_F1
 
@@ -98,7 +100,17 @@ template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type ro
   __device__ __forceinline__ typename fres<rank2<A, B>::n>::type NAME(const A& a, const B& b) { \
     return map2<typename fres<rank2<A, B>::n>::type>([](float x, float y) { return (EXPR); }, a, b); \
   }
-IXB_OP_F2(truediv, x / y)
+// division by a value that does not vary along the vector (a row statistic) is one
+// reciprocal and N multiplies
+template <class A, class B>
+__device__ __forceinline__ typename fres<rank2<A, B>::n>::type truediv(const A& a, const B& b) {
+  if constexpr (rank<B>::n == 0 && rank<A>::n > 0) {
+    const float inv = 1.f / (float)at(b, 0);
+    return map1<typename fres<rank<A>::n>::type>([inv](float x) { return x * inv; }, a);
+  } else {
+    return map2<typename fres<rank2<A, B>::n>::type>([](float x, float y) { return x / y; }, a, b);
+  }
+}
 IXB_OP_F2(pow, powf(x, y))
 IXB_OP_F2(fmod, fmodf(x, y))
 IXB_OP_F2(atan2, atan2f(x, y))
@@ -128,6 +140,16 @@ IXB_OP_ARITH2(truncdiv, truncf(x / y), x / y)
 IXB_OP_ARITH2(remainder, (x - y * floorf(x / y)), ((x % y) + (((x % y) != 0 && ((x % y) < 0) != (y < 0)) ? y : 0)))
 IXB_OP_ARITH2(mod, fmodf(x, y), x % y)
 #undef IXB_OP_ARITH2
+
+// index arithmetic: operands are non-negative, so C truncation equals floor
+template <class A, class B>
+__device__ __forceinline__ typename ires<rank2<A, B>::n>::type idiv(const A& a, const B& b) {
+  return map2<typename ires<rank2<A, B>::n>::type>([](long long x, long long y) { return x / y; }, a, b);
+}
+template <class A, class B>
+__device__ __forceinline__ typename ires<rank2<A, B>::n>::type imod(const A& a, const B& b) {
+  return map2<typename ires<rank2<A, B>::n>::type>([](long long x, long long y) { return x % y; }, a, b);
+}
 
 #define IXB_OP_B2(NAME, EXPR)                                                                  \
   template <class A, class B>                                                                  \

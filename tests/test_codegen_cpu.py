@@ -76,6 +76,19 @@ def test_permuted_store_falls_back_to_scatter_or_gather(dry_backend):
     assert "gather(" in code or "scatter(" in code
 
 
+def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backend):
+    """Reduced axes are not innermost (reference case test_reduction_permute): adjacent
+    threads must walk adjacent outputs, not the strided reduction axis."""
+    x = torch.randn(4, 8, 16, 64).half()
+    code = generated(lambda t: t.permute(0, 3, 1, 2).amax((2, 3)), x)
+    assert code.count("ixb_load_kernel('''") == 1
+    assert "launch_outer_gen<Body>" in code and "family='outer'" in code
+    assert "c.template combine<ixb::MaxOp>(acc)" in code
+    # an inner-axis reduction of the same tensor keeps the row mapping
+    code = generated(lambda t: t.amax(-1), x)
+    assert "launch_row_gen<" in code and "launch_outer_gen" not in code
+
+
 def test_index_analysis():
     from inductor_x_b200.codegen import ir
     from torch.utils._sympy.functions import FloorDiv, ModularIndexing
