@@ -13,6 +13,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import subprocess
 import threading
 import time
@@ -78,8 +79,26 @@ class GeneratedKernel:
         print(f"{self.meta.get('name', self.key)}: {ms:.3f}ms    {gb:.3f}GB    {gb / (ms / 1e3):.2f}GB/s")
 
 
+_headers_digest = None
+
+
+def _template_digest() -> bytes:
+    """Digest of the template headers a generated module includes: editing a header must
+    not resurrect modules compiled against the old one from the on-disk cache."""
+    global _headers_digest
+    if _headers_digest is None:
+        h = hashlib.sha256()
+        inc = os.path.join(_CSRC, "ixb")
+        for name in sorted(os.listdir(inc)):
+            if name.endswith((".cuh", ".h")):
+                with open(os.path.join(inc, name), "rb") as f:
+                    h.update(name.encode() + b"\0" + f.read())
+        _headers_digest = h.digest()
+    return _headers_digest
+
+
 def source_key(src: str) -> str:
-    return hashlib.sha256(src.encode()).hexdigest()[:24]
+    return hashlib.sha256(_template_digest() + src.encode()).hexdigest()[:24]
 
 
 def compile_source(src: str, verbose: bool = False) -> str:
@@ -93,11 +112,23 @@ def compile_source(src: str, verbose: bool = False) -> str:
     with open(cu, "w") as f:
         f.write(src)
     tmp = f"{so}.{os.getpid()}.tmp"
-    cmd = ["nvcc", *_NVCC_FLAGS, "-I", _CSRC, "-o", tmp, cu]
     t0 = time.time()
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed for generated kernel {cu}:\n{proc.stderr[-4000:]}")
+    # A row module states how many CTAs per SM its registers are bounded for.  If ptxas had
+    # to spill under that bound the module is rebuilt with a looser one.
+    m = re.search(r"#define IXB_GEN_MIN_CTAS (\d+)", src)
+    bounds = [None]
+    if m:
+        n = int(m.group(1))
+        bounds = [n] + [b for b in (6, 4, 3, 2, 1) if b < n]
+    for bound in bounds:
+        extra = [] if bound is None else [f"-DIXB_GEN_MIN_CTAS={bound}"]
+        cmd = ["nvcc", *_NVCC_FLAGS, "-Xptxas", "-v", *extra, "-I", _CSRC, "-o", tmp, cu]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed for generated kernel {cu}:\n{proc.stderr[-4000:]}")
+        spills = [int(x) for x in re.findall(r"(\d+) bytes spill stores", proc.stderr)]
+        if bound in (None, 1) or not any(spills):
+            break
     os.replace(tmp, so)
     if verbose:
         print(f"compiled {so} in {time.time() - t0:.1f}s")

@@ -60,6 +60,7 @@ class B200Kernel(SIMDKernel):
         self._row_cfg: Optional[split_tiling.RowConfig] = None
         self._ph: dict = {}
         self._ph_by_key: dict = {}
+        self._row_prefetch: list = []
         self.x_indexing = IndentedBuffer()
         self.r_indexing = IndentedBuffer()
         super().__init__(tiling, **kwargs)
@@ -67,7 +68,7 @@ class B200Kernel(SIMDKernel):
         if self.is_row:
             rnumel = self._static_numel("r0_")
             dt = self._narrowest_node_dtype()
-            self._row_cfg = split_tiling.choose_row_config(rnumel, dt)
+            self._row_cfg = split_tiling.choose_row_config(rnumel, dt, rows=self._static_numel("x"))
             if self._row_cfg is None:
                 raise UnsupportedByTemplates(
                     f"reduced extent {rnumel} does not fit the persistent row template")
@@ -208,7 +209,10 @@ class B200Kernel(SIMDKernel):
         vector_row = has_r or indirect
         row_text = gather.replace("@M@", "rmask" if vector_row else "true")
         if stride == 1 and not masked:
-            row_text = f"c.load_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)))"
+            row_ptr = f"({var}) + ({G}lane0({idx}) - {G}lane0(r0_index))"
+            row_text = f"c.load_row({row_ptr})"
+            if xr.symbol() in exp.free_symbols and row_ptr not in self._row_prefetch:
+                self._row_prefetch.append(row_ptr)     # streamed once per row: worth prefetching
         outer_text = gather.replace("@M@", "xmask")
         x_contig = False
         if not indirect and not masked and xr.symbol() in exp.free_symbols:
@@ -241,7 +245,7 @@ class B200Kernel(SIMDKernel):
         xr, rr = self._xr_roots()
         has_r = rr is not None and rr.symbol() in exp.free_symbols
         vector_row = has_r or indirect
-        row_text = f"{G}scatter({var}, {idx}, {'rmask' if vector_row else '(c.lane == 0)'}, {value});"
+        row_text = f"{G}scatter({var}, {idx}, {'rmask' if vector_row else 'c.leader()'}, {value});"
         if not indirect and has_r and self.inside_reduction:
             stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
                                                self._static_numel("r0_"))
@@ -270,12 +274,24 @@ class B200Kernel(SIMDKernel):
         key = (src_dtype, reduction_type, value)
         if key in self.cse.reduction_cache:
             return self.cse.reduction_cache[key]
-        if reduction_type == "welford_reduce":
+        if reduction_type == "welford_reduce" and not ixb_config.merged_welford:
             result = self.welford_reduce_fallback(dtype, value)
-        elif reduction_type == "online_softmax_reduce":
-            # (row max, sum of exp(value - max)): the row is in registers, so the two-pass
-            # form costs no extra memory traffic
+        elif reduction_type == "online_softmax_reduce" and not ixb_config.merged_online_softmax:
             result = self.prepare_softmax_twopass_fallback(dtype, value)
+        elif reduction_type == "welford_reduce":
+            # (mean, m2, weight) from one exchange of merged partial statistics
+            tag = self._placeholder("R", None, f"c.welford({value})", "", outer_ok=False)
+            self.compute.writeline(f"@B{tag[2:]}")
+            w = self.cse.generate(self.compute, tag, dtype=torch.float32)
+            result = tuple(self.cse.generate(self.compute, f"{w}.{field}", dtype=torch.float32)
+                           for field in ("mean", "m2", "weight"))
+        elif reduction_type == "online_softmax_reduce":
+            # (row max, sum of exp(value - max)) from one exchange of rescaled partial sums
+            tag = self._placeholder("R", None, f"c.online_softmax({value})", "", outer_ok=False)
+            self.compute.writeline(f"@B{tag[2:]}")
+            ms = self.cse.generate(self.compute, tag, dtype=torch.float32)
+            result = tuple(self.cse.generate(self.compute, f"{ms}.{field}", dtype=torch.float32)
+                           for field in ("max", "sum"))
         elif reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
             tag = self._placeholder("R", None, f"c.template reduce_arg<{is_max}>({value})", "", outer_ok=False)
@@ -382,6 +398,11 @@ class B200Kernel(SIMDKernel):
 
         src = IndentedBuffer()
         src.writeline('#include "ixb/gen.cuh"')
+        if self.is_row and not outer:
+            # register bound; the module loader rebuilds with a smaller value on spills
+            src.writeline("#ifndef IXB_GEN_MIN_CTAS")
+            src.writeline(f"#define IXB_GEN_MIN_CTAS {self._row_cfg.min_ctas}")
+            src.writeline("#endif")
         src.writeline("namespace {")
         src.writeline("using namespace ixb;")
         src.writeline("struct Body {")
@@ -428,6 +449,17 @@ class B200Kernel(SIMDKernel):
                     src.splice(r_idx)
                     src.splice(re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False)))
                 src.writeline("}")
+                # L2 prefetch of the streamed operands of a later row
+                src.writeline("template <class Ctx>")
+                src.writeline("__device__ __forceinline__ void prefetch(Ctx& c, const long long xindex) const {")
+                with src.indent():
+                    if self._row_prefetch:
+                        src.writeline("const auto r0_index = c.rindex();")
+                        src.splice(x_idx)
+                        src.splice(r_idx)
+                        for ptr in self._row_prefetch:
+                            src.writeline(f"c.prefetch_row({ptr});")
+                src.writeline("}")
             else:
                 src.writeline(f"static constexpr int kVec = {self.vec};")
                 src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid) const {")
@@ -453,8 +485,9 @@ class B200Kernel(SIMDKernel):
                 narrow = self._narrowest_node_dtype()
                 if cfg.vec == 8 and narrow == torch.float16:
                     rt = "ixb::f16"
-                src.writeline(f"return {G}launch_row_gen<Body, {rt}, {cfg.team}, {cfg.teams}, {cfg.vpt}>"
-                              f"(b, {xnumel}LL, {rnumel}, stream);")
+                full = "true" if cfg.capacity == rnumel else "false"   # no ragged tail to test for
+                src.writeline(f"return {G}launch_row_gen<Body, {rt}, {cfg.team}, {cfg.teams}, {cfg.vpt}, "
+                              f"IXB_GEN_MIN_CTAS, {cfg.prefetch}, {full}>(b, {xnumel}LL, {rnumel}, stream);")
             else:
                 src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream);")
         src.writeline("}")

@@ -23,17 +23,14 @@ import torch
 
 from .. import config
 
-# (team, vpt) pairs, same list as the prebuilt library dispatches over (csrc/host.h)
-ROW_PAIRS = [(32, 1), (32, 2), (32, 4), (64, 4), (128, 2), (128, 4), (256, 2), (256, 4),
-             (512, 2), (512, 4), (1024, 4), (1024, 8)]
-
-
 @dataclasses.dataclass(frozen=True)
 class RowConfig:
-    team: int      # threads cooperating on one row
-    teams: int     # rows processed concurrently by one CTA
-    vpt: int       # 128-bit vectors per thread
-    vec: int       # elements per vector
+    team: int          # threads cooperating on one row
+    teams: int         # rows processed concurrently by one CTA
+    vpt: int           # 128-bit vectors per thread
+    vec: int           # elements per vector
+    min_ctas: int = 1  # resident CTAs per SM the register allocation is bounded for
+    prefetch: int = 0  # rows ahead whose streamed operands are prefetched into L2
 
     @property
     def elems_per_thread(self) -> int:
@@ -55,27 +52,43 @@ def narrowest_dtype(dtypes: Iterable[torch.dtype]) -> torch.dtype:
     return best or torch.float32
 
 
-def choose_row_config(rnumel: int, dtype: torch.dtype, max_vpt: int = 4) -> Optional[RowConfig]:
-    """Smallest team that covers a row of ``rnumel`` elements of ``dtype`` with at most
-    ``max_vpt`` vectors per thread (generated bodies keep several fp32 copies of the row in
-    registers, hence the tighter default than the prebuilt bodies).  None if the row does
-    not fit on chip."""
-    vec = max(config.get_aligned_numel(dtype), 1)
-    vec = min(vec, 8)
+MAX_TEAM = 1024
+MIN_TEAM = 8          # teams narrower than a warp serve rows of a few vectors
+MAX_VPT = 8
+
+
+def choose_row_config(rnumel: int, dtype: torch.dtype, rows: Optional[int] = None,
+                      target_vpt: int = 2) -> Optional[RowConfig]:
+    """Launch shape of a generated persistent-row kernel.
+
+    A generated body keeps several fp32 copies of its part of the row live, so the row is
+    spread thin: ``target_vpt`` vectors per thread over the smallest power-of-two team
+    that covers it (measured on the softmax->LayerNorm chain at 4096 bf16 columns: 256
+    threads x 2 vectors ran 1.2-2x faster than 128 x 4).  Only rows longer than 1024
+    threads x ``target_vpt`` vectors take more per thread, and rows of a few vectors get
+    teams of 8 or 16 lanes so that a warp works on several rows at once.  CTAs hold 128 threads or one
+    team, whichever is larger, and the register allocation is bounded for 1024 resident
+    threads per SM (the module loader relaxes the bound if that makes the body spill).
+    Rows that are streamed long enough get an L2 prefetch two rows ahead.  None if the
+    row does not fit on chip."""
+    vec = min(max(config.get_aligned_numel(dtype), 1), 8)
     nvec = -(-rnumel // vec)
-    best = None
-    for team, vpt in ROW_PAIRS:
-        if vpt > max_vpt and not (team == 1024 and vpt == 8):
-            continue
-        cap = team * vpt
-        if cap < nvec:
-            continue
-        if best is None or cap < best[0] * best[1]:
-            best = (team, vpt)
-    if best is None:
+    if nvec > MAX_TEAM * MAX_VPT:
         return None
-    team, vpt = best
-    return RowConfig(team=team, teams=max(1, 256 // team), vpt=vpt, vec=vec)
+    vpt = target_vpt
+    team = MIN_TEAM
+    while team < MAX_TEAM and team * vpt < nvec:
+        team *= 2
+    while team * vpt < nvec:
+        vpt *= 2
+    while vpt > 1 and team * (vpt // 2) >= nvec:   # short rows: no idle vectors
+        vpt //= 2
+    teams = max(1, 128 // team)
+    min_ctas = max(1, 1024 // (team * teams))
+    row_bytes = rnumel * config.byte_per_numel(dtype) if dtype in config.BYTES_PER_ELEMENT else rnumel * 4
+    streamed = rows is None or rows * row_bytes >= (64 << 20)
+    return RowConfig(team=team, teams=teams, vpt=vpt, vec=vec, min_ctas=min_ctas,
+                     prefetch=2 if streamed and row_bytes >= 2048 else 0)
 
 
 def choose_pointwise_vec(dtypes: Iterable[torch.dtype]) -> int:

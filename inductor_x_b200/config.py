@@ -17,6 +17,13 @@ profile_bandwidth = os.environ.get("IXB_PROFILE_BANDWIDTH", "0") == "1"
 #: keep Inductor's own multi-layer split of long reductions (the reference forces
 #: num_splits == 1, inductor_x/codegen/ir.py:13-24)
 allow_multilayer_reduction = True
+#: one exchange for LayerNorm-style (mean, m2) statistics by merging partial statistics,
+#: and one for softmax's (max, sum of exp), instead of one exchange per plain reduction.
+#: Off by default: on the bf16 softmax->LayerNorm chain at 16384 x 4096 the merged forms
+#: measured slower (106 us -> 151 us and 115 us) - the extra shuffles and divisions of the
+#: merge cost more than the barrier they save.
+merged_welford = os.environ.get("IXB_MERGED_WELFORD", "0") == "1"
+merged_online_softmax = os.environ.get("IXB_MERGED_ONLINE_SOFTMAX", "0") == "1"
 #: compile generated kernels but never launch them (host-logic tests without a GPU)
 dry_run = os.environ.get("IXB_DRY_RUN", "0") == "1"
 #: where generated functor modules are cached

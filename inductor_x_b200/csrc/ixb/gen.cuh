@@ -200,10 +200,22 @@ template <class Body> int launch_pointwise(const Body& body, long long xnumel, v
 // ---- persistent row family ---------------------------------------------------------------
 // The generated body sees a context that maps vector element e = i * kVec + j of this
 // thread to column vec_col(i) + j of the row, exactly as RowCtx does for the prebuilt bodies.
-template <typename T, int TEAM, int TEAMS, int VPT> struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
+// FULL: the row fills every vector of the team exactly (length == TEAM * VPT * kVec), so no
+// element needs a validity test.
+template <typename T, int TEAM, int TEAMS, int VPT, bool FULL = false>
+struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   using Base = RowCtx<T, TEAM, TEAMS, VPT, false>;
   static constexpr int kE = VPT * Base::kVec;
+  static constexpr int kGroup = TEAM < 32 ? TEAM : 32;  // lanes of one warp that share a row
+  // Teams narrower than a warp share their warp's control flow: a team whose row index
+  // ran past the end repeats the last row with `live` false, which masks its stores.
+  bool live = true;
 
+  __device__ __forceinline__ bool leader() const { return this->lane == 0 && live; }
+  // element j of vector i lies inside the row
+  __device__ __forceinline__ bool inside(int i, int j) const {
+    return FULL ? true : (this->vec_col(i) + j < this->cols);
+  }
   __device__ __forceinline__ vi<kE> rindex() const {
     vi<kE> r;
 #pragma unroll
@@ -217,7 +229,7 @@ template <typename T, int TEAM, int TEAMS, int VPT> struct GenRowCtx : RowCtx<T,
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
-      for (int j = 0; j < Base::kVec; ++j) r.v[i * Base::kVec + j] = this->vec_col(i) + j < this->cols;
+      for (int j = 0; j < Base::kVec; ++j) r.v[i * Base::kVec + j] = live && inside(i, j);
     return r;
   }
   // row-contiguous operand of storage type U starting at `rowp`
@@ -227,19 +239,31 @@ template <typename T, int TEAM, int TEAMS, int VPT> struct GenRowCtx : RowCtx<T,
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c0 = this->vec_col(i);
-      const int left = this->cols - c0;
+      const int left = FULL ? Base::kVec : this->cols - c0;
       auto part = ldvec<U, Base::kVec>(rowp + c0, left > 0 ? left : 0);
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j) r.v[i * Base::kVec + j] = part.v[j];
     }
     return r;
   }
-  template <class U, class A> __device__ __forceinline__ void store_row(U* rowp, const A& val) const {
-    using V = typename Mem<U>::val;
+  // ask L2 for the lines of a row-contiguous operand this thread will load later: the
+  // thread whose vector opens a 128-byte line (or the row itself) issues the prefetch
+  template <class U> __device__ __forceinline__ void prefetch_row(const U* rowp) const {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c0 = this->vec_col(i);
-      const int left = this->cols - c0;
+      const U* p = rowp + c0;
+      const bool opens = (reinterpret_cast<unsigned long long>(p) & 127ull) < Base::kVec * sizeof(U) || c0 == 0;
+      if (c0 < this->cols && opens) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+    }
+  }
+  template <class U, class A> __device__ __forceinline__ void store_row(U* rowp, const A& val) const {
+    using V = typename Mem<U>::val;
+    if (!live) return;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c0 = this->vec_col(i);
+      const int left = FULL ? Base::kVec : this->cols - c0;
       typename vec_of<V, Base::kVec>::type part;
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j) part.v[j] = Cast<V>::from(at(val, i * Base::kVec + j));
@@ -253,9 +277,10 @@ template <typename T, int TEAM, int TEAMS, int VPT> struct GenRowCtx : RowCtx<T,
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j)
-        if (this->vec_col(i) + j < this->cols)
+        if (inside(i, j))
           acc = Op::combine(acc, Cast<float>::from(at(val, i * Base::kVec + j)));
-    return Base::template reduce<Op>(acc);
+    if constexpr (TEAM < 32) return lane_group_reduce<Op, TEAM>(acc);
+    else return Base::template reduce<Op>(acc);
   }
   template <bool IS_MAX, class A> __device__ __forceinline__ long long reduce_arg(const A& val) {
     ArgPair best = ArgOp<IS_MAX>::identity();
@@ -263,34 +288,143 @@ template <typename T, int TEAM, int TEAMS, int VPT> struct GenRowCtx : RowCtx<T,
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j)
-        if (this->vec_col(i) + j < this->cols)
+        if (inside(i, j))
           best = ArgOp<IS_MAX>::combine(
               best, ArgPair{Cast<float>::from(at(val, i * Base::kVec + j)), (long long)(this->vec_col(i) + j)});
-    return Base::template reduce_arg<IS_MAX>(best).i;
+    if constexpr (TEAM < 32) {
+#pragma unroll
+      for (int o = TEAM / 2; o > 0; o >>= 1) {
+        ArgPair q;
+        q.v = __shfl_xor_sync(kFull, best.v, o);
+        q.i = __shfl_xor_sync(kFull, best.i, o);
+        best = ArgOp<IS_MAX>::combine(best, q);
+      }
+      return best.i;
+    } else {
+      return Base::template reduce_arg<IS_MAX>(best).i;
+    }
+  }
+  // (row maximum, sum of exp(value - maximum)) with a single exchange: every thread sums
+  // relative to its own maximum and the partial sums are rescaled as they are folded
+  struct MaxSum {
+    float max, sum;
+  };
+  template <class A> __device__ __forceinline__ MaxSum online_softmax(const A& val) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j)) m = fmaxf(m, Cast<float>::from(at(val, i * Base::kVec + j)));
+    if constexpr (TEAM < 32) m = lane_group_reduce<MaxOp, TEAM>(m);  // no exchange to save: plain two-step
+    float s[1] = {0.f}, none[1] = {0.f};
+    const float shift = (m == -INFINITY) ? 0.f : m;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j))
+          s[0] += fast_exp2((Cast<float>::from(at(val, i * Base::kVec + j)) - shift) * kLog2e);
+    if constexpr (TEAM < 32) s[0] = lane_group_reduce<SumOp, TEAM>(s[0]);
+    else Base::template reduce_rescaled<1, 0>(m, s, none, kLog2e);
+    return MaxSum{m, s[0]};
+  }
+  // (mean, sum of squared deviations, count) of the row with a single exchange: each
+  // thread forms the statistics of its own elements and partial statistics are merged
+  // pairwise (Chan et al.), which stays accurate when the mean is large against the spread
+  struct Welford {
+    float mean, m2, weight;
+  };
+  static __device__ __forceinline__ Welford merge(const Welford& a, const Welford& b) {
+    const float n = a.weight + b.weight;
+    const float w = n > 0.f ? __fdividef(b.weight, n) : 0.f;
+    const float d = b.mean - a.mean;
+    return Welford{fmaf(d, w, a.mean), a.m2 + b.m2 + d * d * a.weight * w, n};
+  }
+  template <class A> __device__ __forceinline__ Welford welford(const A& val) {
+    float n = 0.f, sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j)) {
+          n += 1.f;
+          sum += Cast<float>::from(at(val, i * Base::kVec + j));
+        }
+    Welford w{n > 0.f ? sum / n : 0.f, 0.f, n};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j)) {
+          const float d = Cast<float>::from(at(val, i * Base::kVec + j)) - w.mean;
+          w.m2 = fmaf(d, d, w.m2);
+        }
+#pragma unroll
+    for (int off = kGroup / 2; off > 0; off >>= 1) {
+      Welford o{__shfl_xor_sync(0xffffffffu, w.mean, off), __shfl_xor_sync(0xffffffffu, w.m2, off),
+                __shfl_xor_sync(0xffffffffu, w.weight, off)};
+      // both lanes of a pair must fold in the same order to agree bit for bit
+      w = (this->lane & off) ? merge(o, w) : merge(w, o);
+    }
+    if constexpr (TEAM > 32) {
+      float* slot = this->red + this->phase * Base::kWarpsPerTeam * 4;
+      if ((this->lane & 31) == 0)
+        *reinterpret_cast<float4*>(slot + (this->lane >> 5) * 4) = make_float4(w.mean, w.m2, w.weight, 0.f);
+      team_barrier(this->team + 1, TEAM);
+      const float4 first = *reinterpret_cast<const float4*>(slot);
+      w = Welford{first.x, first.y, first.z};
+#pragma unroll
+      for (int k = 1; k < Base::kWarpsPerTeam; ++k) {
+        const float4 part = *reinterpret_cast<const float4*>(slot + k * 4);
+        w = merge(w, Welford{part.x, part.y, part.z});
+      }
+      this->phase ^= 1;
+    }
+    return w;
   }
   template <class A> __device__ __forceinline__ bool reduce_any(const A& val) {
     return reduce<MaxOp>(op::where(val, 1.f, 0.f)) != 0.f;
   }
 };
 
-template <class Body, typename T, int TEAM, int TEAMS, int VPT>
-__global__ void __launch_bounds__(TEAM* TEAMS)
+template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS, int PF, bool FULL>
+__global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
     row_gen_kernel(const Body body, const long long rows, const int cols) {
-  using Ctx = GenRowCtx<T, TEAM, TEAMS, VPT>;
-  __shared__ __align__(16) float exchange[TEAMS * 2 * (TEAM / 32) * 4];
+  using Ctx = GenRowCtx<T, TEAM, TEAMS, VPT, FULL>;
+  constexpr int kSlots = TEAM > 32 ? 2 * (TEAM / 32) * 4 : 1;  // exchange floats per team
+  __shared__ __align__(16) float exchange[TEAMS * kSlots];
   Ctx c;
   c.lane = threadIdx.x % TEAM;
   c.team = threadIdx.x / TEAM;
   c.cols = cols;
   c.phase = 0;
-  c.red = exchange + c.team * 2 * (TEAM / 32) * 4;
+  c.red = exchange + c.team * kSlots;
   const long long stride = (long long)gridDim.x * TEAMS;
-  for (long long r = (long long)blockIdx.x * TEAMS + c.team; r < rows; r += stride) body.row(c, r);
+  if constexpr (TEAM < 32) {
+    // the teams of a warp run the same number of rows (full-mask shuffles inside)
+    for (long long base = (long long)blockIdx.x * TEAMS; base < rows; base += stride) {
+      const long long r = base + c.team;
+      c.live = r < rows;
+      body.row(c, c.live ? r : rows - 1);
+    }
+    return;
+  }
+  for (long long r = (long long)blockIdx.x * TEAMS + c.team; r < rows; r += stride) {
+    // PF rows ahead of the one being worked on are on their way from DRAM to L2
+    if constexpr (PF > 0) {
+      const long long ahead = r + PF * stride;
+      if (ahead < rows) body.prefetch(c, ahead);
+    }
+    body.row(c, r);
+  }
 }
-template <class Body, typename T, int TEAM, int TEAMS, int VPT>
+template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS = 1, int PF = 0, bool FULL = false>
 int launch_row_gen(const Body& body, long long rows, int cols, void* stream) {
   if (rows <= 0) return 0;
-  auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT>;
+  if (FULL && cols != TEAM * VPT * Elem<T>::kVec) return (int)cudaErrorInvalidValue;
+  auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL>;
   static int resident = 0;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -83,9 +83,20 @@ template <typename T, int TEAM, int TEAMS, int VPT, bool ALIGNED> struct RowCtx 
       float* slot = red + phase * kWarpsPerTeam * 4;
       if ((lane & 31) == 0) slot[lane >> 5] = v;
       team_barrier(team + 1, TEAM);
-      v = slot[0];
+      if constexpr (kWarpsPerTeam % 4 == 0) {
+        // the partials of four warps per 128-bit shared load
+        const float4 q0 = *reinterpret_cast<const float4*>(slot);
+        v = Op::combine(Op::combine(q0.x, q0.y), Op::combine(q0.z, q0.w));
 #pragma unroll
-      for (int w = 1; w < kWarpsPerTeam; ++w) v = Op::combine(v, slot[w]);
+        for (int w = 4; w < kWarpsPerTeam; w += 4) {
+          const float4 q = *reinterpret_cast<const float4*>(slot + w);
+          v = Op::combine(v, Op::combine(Op::combine(q.x, q.y), Op::combine(q.z, q.w)));
+        }
+      } else {
+        v = slot[0];
+#pragma unroll
+        for (int w = 1; w < kWarpsPerTeam; ++w) v = Op::combine(v, slot[w]);
+      }
       phase ^= 1;
     }
     return v;

@@ -49,7 +49,7 @@ def test_c1_graph_is_one_row_kernel(dry_backend):
     code = generated(lambda x, w, b: F.gelu(x * w + b).sum(-1), torch.randn(64, 1024), torch.randn(1024),
                      torch.randn(1024))
     assert code.count("ixb_load_kernel('''") == 1
-    assert "launch_row_gen<Body, float, 64, 4, 4>" in code          # 1024 fp32 = 256 vectors
+    assert "launch_row_gen<Body, float, 128, 1, 2, IXB_GEN_MIN_CTAS, 0, true>" in code   # 1024 fp32 = 256 vectors
     assert code.count("c.load_row(") == 3 and "reduce<ixb::SumOp>" in code
     assert "triton" not in code.split("ixb_load_kernel")[1]
 
@@ -58,8 +58,9 @@ def test_c2_chain_is_one_row_kernel_with_four_reductions(dry_backend):
     fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5)
     code = generated(fn, torch.randn(32, 4096).bfloat16(), *(torch.randn(4096).bfloat16() for _ in range(3)))
     assert code.count("ixb_load_kernel('''") == 1
-    assert "launch_row_gen<Body, ixb::bf16, 128, 2, 4>" in code      # 4096 bf16 = 512 vectors
-    assert len(re.findall(r"c\.template reduce<", code)) == 4
+    assert "launch_row_gen<Body, ixb::bf16, 256, 1, 2, IXB_GEN_MIN_CTAS, 0, true>" in code   # 4096 bf16 = 512 vectors
+    assert len(re.findall(r"c\.template reduce<", code)) == 4      # max, sum(exp), mean, variance
+    assert "c.prefetch_row(" in code
     assert "c.store_row(" in code
 
 
@@ -110,10 +111,15 @@ def test_index_analysis():
 def test_launch_chooser():
     from inductor_x_b200.codegen import split_tiling as st
 
-    c = st.choose_row_config(4096, torch.bfloat16)
-    assert (c.team, c.vpt, c.vec, c.teams) == (128, 4, 8, 2) and c.capacity >= 4096
+    c = st.choose_row_config(4096, torch.bfloat16, rows=16384)
+    assert (c.team, c.vpt, c.vec, c.teams, c.min_ctas, c.prefetch) == (256, 2, 8, 1, 4, 2)
+    assert st.choose_row_config(4096, torch.bfloat16, rows=32).prefetch == 0    # nothing to stream
     c = st.choose_row_config(1000, torch.float32)
-    assert c.capacity >= 1000 and c.vec == 4
+    assert c.capacity >= 1000 and c.vec == 4 and (c.team, c.vpt) == (128, 2)
+    c = st.choose_row_config(64, torch.float16)                      # 8 vectors: a quarter warp per row
+    assert (c.team, c.vpt, c.teams) == (8, 1, 16)
+    c = st.choose_row_config(32768, torch.float32)                   # beyond 1024 x 2 vectors
+    assert (c.team, c.vpt) == (1024, 8)
     assert st.choose_row_config(1 << 20, torch.float32) is None
     assert st.choose_pointwise_vec([torch.float32, torch.bfloat16]) == 8
     assert st.choose_pointwise_vec([torch.float32]) == 4
