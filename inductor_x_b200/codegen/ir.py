@@ -12,9 +12,11 @@ CUDA templates need the same two facts in a different form:
 * is an access *contiguous along the reduced row* (row template) - and if not, what is the
   stride of the reduced variable (outer reduction).
 
-Both are answered on the expression expanded back to the root index variables, by exact
-integer evaluation at sample points (the expressions are piecewise-affine in the roots, so
-sampled agreement on aligned groups is decisive for the static shapes handled here).
+Both are answered on the expression expanded back to the root index variables.  The
+vector questions are decided structurally (``vector_access``): the expression must be a sum
+of integer multiples of ``root``, ``ModularIndexing(root, d, m)`` and ``FloorDiv(root, d)``
+whose break points all fall on vector boundaries, which makes it affine inside every
+aligned vector; exact evaluation at sample points then cross-checks the verdict.
 """
 from __future__ import annotations
 
@@ -53,6 +55,71 @@ def _sample_bases(numel: int, group: int, n: int = 12) -> Iterable[int]:
     return [g * group for g in sorted(picks) if 0 <= g < groups]
 
 
+def vector_access(expr: sympy.Expr, root: sympy.Symbol, vec: int):
+    """(contiguous, aligned) of the ``vec`` elements ``root = b .. b + vec - 1`` for every
+    ``b`` that is a multiple of ``vec``, decided from the structure of ``expr``; (False,
+    False) when the structure is not one this analysis understands.
+
+    contiguous: ``expr(b + k) == expr(b) + k``; aligned: ``expr(b)`` is a multiple of
+    ``vec``.  Symbols other than ``root`` (the reduced index of an outer reduction) may
+    appear in terms that do not involve ``root``; such terms must carry a coefficient that
+    is a multiple of ``vec`` for the access to count as aligned."""
+    from torch.utils._sympy.functions import FloorDiv, ModularIndexing
+
+    unit = 0          # total coefficient of the terms that advance by one per element
+    aligned = True
+    for term in sympy.Add.make_args(sympy.expand(expr)):
+        coeff, atom = term.as_coeff_Mul()
+        if not coeff.is_Integer:
+            return False, False
+        coeff = int(coeff)
+        if atom == 1:
+            aligned &= coeff % vec == 0
+        elif root not in atom.free_symbols:
+            aligned &= coeff % vec == 0           # any integer-valued function of other symbols
+        elif atom == root:
+            unit += coeff
+        elif isinstance(atom, ModularIndexing) and atom.args[0] == root and all(a.is_Integer for a in atom.args[1:]):
+            d, m = int(atom.args[1]), int(atom.args[2])
+            if d % vec == 0:
+                aligned &= coeff % vec == 0       # constant inside a vector
+            elif d == 1 and m % vec == 0:
+                unit += coeff                     # advances without wrapping inside a vector
+            else:
+                return False, False
+        elif isinstance(atom, FloorDiv) and atom.args[0] == root and atom.args[1].is_Integer:
+            if int(atom.args[1]) % vec != 0:
+                return False, False
+            aligned &= coeff % vec == 0
+        else:
+            return False, False
+    return unit == 1, bool(aligned and unit == 1)
+
+
+def is_vector_constant(expr: sympy.Expr, root: sympy.Symbol, vec: int) -> bool:
+    """True when ``expr`` takes one value over every aligned group of ``vec`` consecutive
+    values of ``root`` (for instance ``FloorDiv(root, 128)`` with ``vec`` 8)."""
+    from torch.utils._sympy.functions import FloorDiv, ModularIndexing
+
+    if expr.free_symbols - {root}:
+        return False
+    for term in sympy.Add.make_args(sympy.expand(expr)):
+        coeff, atom = term.as_coeff_Mul()
+        if not coeff.is_Integer:
+            return False
+        if atom == 1:
+            continue
+        if isinstance(atom, ModularIndexing) and atom.args[0] == root and all(a.is_Integer for a in atom.args[1:]):
+            if int(atom.args[1]) % vec != 0:
+                return False
+        elif isinstance(atom, FloorDiv) and atom.args[0] == root and atom.args[1].is_Integer:
+            if int(atom.args[1]) % vec != 0:
+                return False
+        else:
+            return False
+    return True
+
+
 def is_vector_contiguous(expr: sympy.Expr, root: sympy.Symbol, vec: int, numel: int) -> bool:
     """True when, for every flat position b that is a multiple of ``vec``,
     ``expr(b + k) == expr(b) + k`` for k < vec: the ``vec`` elements a thread owns are
@@ -60,6 +127,8 @@ def is_vector_contiguous(expr: sympy.Expr, root: sympy.Symbol, vec: int, numel: 
     if expr.free_symbols - {root}:
         return False
     if numel < vec:
+        return False
+    if not vector_access(expr, root, vec)[0]:
         return False
     for b in _sample_bases(numel, vec):
         if b + vec > numel:

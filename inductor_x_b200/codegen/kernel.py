@@ -161,6 +161,13 @@ class B200Kernel(SIMDKernel):
             table[key] = tag
         return tag
 
+    def _fast_flag(self, exp: sympy.Expr, vec: int) -> str:
+        """Template argument that makes a vector access unconditional in full tiles: the
+        index is proven a multiple of the vector width, so with 16-byte aligned base
+        pointers (checked by the launcher) the address is aligned."""
+        aligned = index_ir.vector_access(exp, self._root("x").symbol(), vec)[1]
+        return "FAST" if aligned else "false"
+
     def _xr_roots(self):
         return self._root("x"), self._root("r0_")
 
@@ -192,10 +199,24 @@ class B200Kernel(SIMDKernel):
 
         if not self.is_row:
             line = gather.replace("@M@", "xmask")
+            xsym = self._root("x").symbol()
+            if indirect and not masked:
+                # direct part contiguous along the vector: one 128-bit access whenever the
+                # indirect operands are per-vector scalars (decided by their C++ type)
+                exp = self._expanded(index)
+                ind = sorted(str(s) for s in exp.free_symbols if str(s).startswith(("tmp", "indirect")))
+                contig, aligned = index_ir.vector_access(exp, xsym, self.vec)
+                if contig and not (exp.free_symbols - {xsym} - {s for s in exp.free_symbols if str(s) in ind}):
+                    al = "FAST" if aligned else "false"
+                    line = (f"{G}igather<{ctype}, kVec, {al}>({var}, {idx}, xmask, {other}, nvalid, "
+                            f"{', '.join(ind)})")
             if not indirect and not masked:
                 exp = self._expanded(index)
+                if xsym in exp.free_symbols and index_ir.is_vector_constant(exp, xsym, self.vec):
+                    line = f"{G}ld_uniform({var}, {G}lane0({idx}), nvalid > 0, {other})"
                 if index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec, self._static_numel("x")):
-                    line = f"{G}ldvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid)"
+                    al = self._fast_flag(exp, self.vec)
+                    line = f"{G}ldvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid)"
             return self.cse.generate(self.compute, line, dtype=val_dtype)
 
         # reduction group: text for both mappings
@@ -218,7 +239,8 @@ class B200Kernel(SIMDKernel):
         if not indirect and not masked and xr.symbol() in exp.free_symbols:
             x_contig = self._outer_x_contiguous(exp)
             if x_contig:
-                outer_text = f"{G}ldvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid)"
+                al = self._fast_flag(exp, self._outer_vec)
+                outer_text = f"{G}ldvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid)"
         tag = self._placeholder("L", (name, idx, str(self._load_mask), other), row_text, outer_text,
                                 stride=stride, has_r=has_r, x_contig=x_contig, indirect=indirect,
                                 in_reduction=self.inside_reduction)
@@ -239,7 +261,8 @@ class B200Kernel(SIMDKernel):
             line = f"{G}scatter({var}, {idx}, xmask, {value});"
             if not indirect and index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec,
                                                               self._static_numel("x")):
-                line = f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), nvalid, {value});"
+                al = self._fast_flag(exp, self.vec)
+                line = f"{G}stvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid, {value});"
             self.compute.writeline(DeferredLine(name, line))
             return
         xr, rr = self._xr_roots()
@@ -421,7 +444,7 @@ class B200Kernel(SIMDKernel):
                     "min": "acc = ixb::gen::op::minimum(acc, ixb::gen::op::to_float({v}));",
                 }[red["rtype"]].format(v=red["value"])
                 src.writeline(f"static constexpr int kVec = {self._outer_vec};")
-                src.writeline("template <class Ctx>")
+                src.writeline("template <bool FAST, class Ctx>")
                 src.writeline("__device__ __forceinline__ void tile(Ctx& c, const long long xbase, const int nvalid) const {")
                 with src.indent():
                     src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
@@ -462,6 +485,7 @@ class B200Kernel(SIMDKernel):
                 src.writeline("}")
             else:
                 src.writeline(f"static constexpr int kVec = {self.vec};")
+                src.writeline("template <bool FAST>")
                 src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid) const {")
                 with src.indent():
                     src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
@@ -477,7 +501,8 @@ class B200Kernel(SIMDKernel):
             for a in assigns:
                 src.writeline(a)
             if outer:
-                src.writeline(f"return {G}launch_outer_gen<Body>(b, {xnumel}LL, stream);")
+                src.writeline(f"return {G}launch_outer_gen<Body>(b, {xnumel}LL, stream, "
+                              f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
             elif self.is_row:
                 cfg = self._row_cfg
                 rnumel = self._static_numel("r0_")
@@ -489,7 +514,8 @@ class B200Kernel(SIMDKernel):
                 src.writeline(f"return {G}launch_row_gen<Body, {rt}, {cfg.team}, {cfg.teams}, {cfg.vpt}, "
                               f"IXB_GEN_MIN_CTAS, {cfg.prefetch}, {full}>(b, {xnumel}LL, {rnumel}, stream);")
             else:
-                src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream);")
+                src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream, "
+                              f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
         src.writeline("}")
         text = src.getvalue()
         return f"ixb_load_kernel('''\n{text}''', family={self.mapping!r})"

@@ -137,14 +137,17 @@ __device__ __forceinline__ void scatter(T* p, const I& idx, const M& mask, const
   }
 }
 
-// contiguous run of N elements starting at p: 128-bit accesses when the address allows
-template <class T, int N>
+// contiguous run of N elements starting at p: 128-bit accesses when the address allows.
+// FAST: the caller knows the run is complete and 16-byte aligned (full tile, aligned base
+// pointer checked on the host, index proven a multiple of the vector), so the access is
+// unconditional - no branch separates the loads of an unrolled loop and they overlap.
+template <class T, int N, bool FAST = false>
 __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(const T* p, int nvalid) {
   using V = typename Mem<T>::val;
   typename vec_of<V, N>::type r;
   constexpr int kPer = 16 / sizeof(T);
   if constexpr ((N % kPer) == 0 && (sizeof(T) == 2 || sizeof(T) == 4) && std::is_same<V, float>::value) {
-    if (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    if (FAST || (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0)) {
 #pragma unroll
       for (int c = 0; c < N / kPer; ++c) unpack<T>(ldg_keep(p + c * kPer), &r.v[c * kPer]);
       return r;
@@ -154,11 +157,12 @@ __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(
   for (int i = 0; i < N; ++i) r.v[i] = i < nvalid ? Mem<T>::ld(p + i) : V();
   return r;
 }
-template <class T, int N, class A> __device__ __forceinline__ void stvec(T* p, int nvalid, const A& val) {
+template <class T, int N, bool FAST = false, class A>
+__device__ __forceinline__ void stvec(T* p, int nvalid, const A& val) {
   using V = typename Mem<T>::val;
   constexpr int kPer = 16 / sizeof(T);
   if constexpr ((N % kPer) == 0 && (sizeof(T) == 2 || sizeof(T) == 4) && std::is_same<V, float>::value) {
-    if (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    if (FAST || (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0)) {
       float f[N];
 #pragma unroll
       for (int i = 0; i < N; ++i) f[i] = Cast<float>::from(at(val, i));
@@ -172,8 +176,36 @@ template <class T, int N, class A> __device__ __forceinline__ void stvec(T* p, i
     if (i < nvalid) Mem<T>::st(p + i, Cast<V>::from(at(val, i)));
 }
 
+// One element shared by all the elements a thread owns (an index or a per-row scale whose
+// address does not change inside a vector): a single load, returned as a scalar, so that
+// everything computed from it is scalar too.
+template <class T>
+__device__ __forceinline__ typename Mem<T>::val ld_uniform(const T* p, long long idx, bool valid,
+                                                           typename Mem<T>::val other) {
+  return valid ? Mem<T>::ld(p + idx) : other;
+}
+// Indirect access whose direct part is contiguous along the vector.  If every indirect
+// operand turned out to be a scalar (it came from ld_uniform), the N elements are adjacent
+// and move as one 128-bit access; otherwise one access per element.
+template <class T, int N, bool FAST, class I, class M, class... U>
+__device__ __forceinline__ auto igather(const T* p, const I& idx, const M& mask, typename Mem<T>::val other,
+                                        int nvalid, const U&... indirect) {
+  if constexpr (((rank<U>::n == 0) && ...) && rank<I>::n == N) {
+    return ldvec<T, N, FAST>(p + at(idx, 0), nvalid);
+  } else {
+    return gather(p, idx, mask, other);
+  }
+}
+
 // ---- pointwise family -------------------------------------------------------------------
-template <class Body>
+// true when every pointer argument of a generated module is 16-byte aligned
+inline bool pointers_aligned(void* const* ptrs, int n) {
+  for (int i = 0; i < n; ++i)
+    if (reinterpret_cast<uintptr_t>(ptrs[i]) & 15u) return false;
+  return true;
+}
+
+template <class Body, bool ALIGNED>
 __global__ void __launch_bounds__(256) pointwise_gen_kernel(const Body body, const long long xnumel) {
   constexpr int V = Body::kVec;
   const long long ntiles = (xnumel + V - 1) / V;
@@ -181,10 +213,11 @@ __global__ void __launch_bounds__(256) pointwise_gen_kernel(const Body body, con
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < ntiles; t += stride) {
     const long long xbase = t * V;
     const long long left = xnumel - xbase;
-    body.tile(xbase, left >= V ? V : (int)left);
+    if (ALIGNED && left >= V) body.template tile<true>(xbase, V);
+    else body.template tile<false>(xbase, left >= V ? V : (int)left);
   }
 }
-template <class Body> int launch_pointwise(const Body& body, long long xnumel, void* stream) {
+template <class Body> int launch_pointwise(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -193,7 +226,8 @@ template <class Body> int launch_pointwise(const Body& body, long long xnumel, v
   long long grid = (ntiles + 255) / 256;
   const long long cap = (long long)sms * 16;  // persistent beyond 16 CTAs per SM
   if (grid > cap) grid = cap;
-  pointwise_gen_kernel<Body><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
+  if (aligned) pointwise_gen_kernel<Body, true><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
+  else pointwise_gen_kernel<Body, false><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
   return (int)cudaGetLastError();
 }
 
@@ -477,7 +511,7 @@ template <int V, int TX, int TY> struct OuterCtx {
   }
 };
 
-template <class Body, int TX, int TY>
+template <class Body, int TX, int TY, bool ALIGNED>
 __global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, const long long xnumel) {
   constexpr int V = Body::kVec;
   __shared__ float part[TY * TX * V];
@@ -490,10 +524,12 @@ __global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, cons
   for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const long long xbase = t * per_cta + (long long)c.tx * V;
     const long long left = xnumel - xbase;
-    body.tile(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
+    // the choice is uniform per warp only if whole CTAs take it: decided on the CTA's tile
+    if (ALIGNED && xnumel - t * per_cta >= per_cta) body.template tile<true>(c, xbase, V);
+    else body.template tile<false>(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
   }
 }
-template <class Body> int launch_outer_gen(const Body& body, long long xnumel, void* stream) {
+template <class Body> int launch_outer_gen(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;
   constexpr int TX = 32, TY = 8;
   int dev = 0, sms = 148;
@@ -503,7 +539,8 @@ template <class Body> int launch_outer_gen(const Body& body, long long xnumel, v
   long long grid = (xnumel + per_cta - 1) / per_cta;
   const long long cap = (long long)sms * 8;
   if (grid > cap) grid = cap;
-  outer_gen_kernel<Body, TX, TY><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
+  if (aligned) outer_gen_kernel<Body, TX, TY, true><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
+  else outer_gen_kernel<Body, TX, TY, false><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
   return (int)cudaGetLastError();
 }
 

@@ -67,7 +67,9 @@ def test_c2_chain_is_one_row_kernel_with_four_reductions(dry_backend):
 def test_pointwise_uses_128bit_access_when_contiguous(dry_backend):
     code = generated(lambda a, b: F.silu(a) * b, torch.randn(8, 1000).bfloat16(), torch.randn(8, 1000).bfloat16())
     assert "launch_pointwise<Body>" in code and "kVec = 8" in code
-    assert code.count("ldvec<ixb::bf16, kVec>") == 2 and "stvec<ixb::bf16, kVec>" in code
+    # unconditional 128-bit access in full tiles: the flat index is a multiple of the vector
+    assert code.count("ldvec<ixb::bf16, kVec, FAST>") == 2 and "stvec<ixb::bf16, kVec, FAST>" in code
+    assert "pointers_aligned(ptrs, 3)" in code
     assert "gather(" not in code
 
 
