@@ -242,7 +242,7 @@ class B200Kernel(SIMDKernel):
                 al = self._fast_flag(exp, self._outer_vec)
                 outer_text = f"{G}ldvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid)"
         tag = self._placeholder("L", (name, idx, str(self._load_mask), other), row_text, outer_text,
-                                stride=stride, has_r=has_r, x_contig=x_contig, indirect=indirect,
+                                stride=stride, has_r=has_r, x_contig=x_contig, indirect=indirect, exp=exp,
                                 in_reduction=self.inside_reduction)
         return self.cse.generate(self.compute, tag, dtype=val_dtype)
 
@@ -405,6 +405,21 @@ class B200Kernel(SIMDKernel):
         used_after = set(re.findall(r"\b(tmp\d+)\b", tail))
         return not (defined & used_after)
 
+    def _outer_tx(self) -> int:
+        """Threads along the kept axis in the outer mapping: as many as the shortest
+        contiguous run among the x-contiguous loads of the reduction holds vectors (so that
+        the remaining lanes of a warp walk the reduced axis), at most a warp."""
+        xsym = self._root("x").symbol()
+        loads = [v for v in self._ph.values() if v["kind"] == "L" and v["has_r"] and v["x_contig"]]
+        tx = 32
+        while tx > 1:
+            span = tx * self._outer_vec
+            if span <= self._static_numel("x") and all(
+                    index_ir.vector_access(v["exp"], xsym, span)[0] for v in loads):
+                break
+            tx //= 2
+        return tx
+
     def _substitute(self, text: str, outer: bool) -> str:
         for tag, v in self._ph.items():
             text = text.replace(tag, v["outer"] if outer else v["row"])
@@ -451,7 +466,7 @@ class B200Kernel(SIMDKernel):
                     src.writeline("const auto xmask = xindex < (xbase + nvalid);")
                     src.splice(x_idx)
                     src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
-                    src.writeline("#pragma unroll 4")  # independent loads of four steps in flight
+                    src.writeline("#pragma unroll 8")  # independent loads of eight steps in flight
                     src.writeline(f"for (long long r0_index = c.ty; r0_index < {rnumel}LL; r0_index += Ctx::kTY) {{")
                     with src.indent():
                         src.splice(r_idx)
@@ -501,7 +516,7 @@ class B200Kernel(SIMDKernel):
             for a in assigns:
                 src.writeline(a)
             if outer:
-                src.writeline(f"return {G}launch_outer_gen<Body>(b, {xnumel}LL, stream, "
+                src.writeline(f"return {G}launch_outer_gen<Body, {self._outer_tx()}>(b, {xnumel}LL, stream, "
                               f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
             elif self.is_row:
                 cfg = self._row_cfg

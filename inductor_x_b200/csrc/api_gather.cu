@@ -19,9 +19,30 @@ int gather_t(const void* table, const void* idx, void* out, int64_t n_rows, int6
     pb.inner = row_bytes;
     ixb_cfg cfg;
     if (int st = ixb_choose_config(&pb, dev, &cfg)) return st;
-    ixb::gather_rows_kernel<IdxT, 4, WRAP><<<cfg.grid, 256, 0, s>>>(
-        (const uint4*)table, (const IdxT*)idx, (uint4*)out, n_rows, m, (int)(row_bytes / 16),
-        pitch / 16, status);
+    const int vpr = (int)(row_bytes / 16);
+    int shift = -1;
+    if ((vpr & (vpr - 1)) == 0)
+      for (shift = 0; (1 << shift) < vpr; ++shift) {}
+    // Persistent launch: exactly the CTAs that are resident at once, each striding over the
+    // vectors.  A grid of a few waves would leave the last wave partly empty.
+    constexpr int kUnroll = 1;
+    auto kern = ixb::gather_rows_kernel<IdxT, kUnroll, WRAP>;
+    static int resident[64] = {};
+    int devid = 0;
+    cudaGetDevice(&devid);
+    int& occ = resident[devid & 63];
+    if (occ == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, 0) != cudaSuccess || n < 1) n = 1;
+      occ = n;
+    }
+    const long long vecs = (long long)m * vpr;
+    long long grid = (vecs + 256LL * kUnroll - 1) / (256LL * kUnroll);
+    const long long cap = (long long)dev->sm_count * occ;
+    if (grid > cap) grid = cap;
+    (void)cfg;
+    kern<<<(unsigned)grid, 256, 0, s>>>(
+        (const uint4*)table, (const IdxT*)idx, (uint4*)out, n_rows, m, vpr, shift, pitch / 16, status);
     return ixb_host::cuda_status(cudaGetLastError());
   }
   // byte-granular fallback: widest element size dividing the row, pitch and pointers

@@ -17,8 +17,11 @@ template <typename IdxT, int UNROLL, bool WRAP_NEGATIVE>
 __global__ void __launch_bounds__(256)
     gather_rows_kernel(const uint4* __restrict__ table, const IdxT* __restrict__ idx,
                        uint4* __restrict__ out, long long n_rows, long long m, int vec_per_row,
-                       long long table_row_vecs, int* __restrict__ status) {
+                       int row_shift, long long table_row_vecs, int* __restrict__ status) {
+  // row_shift = log2(vec_per_row) when that is a power of two, else -1: splitting a flat
+  // vector index into (row, column) must not cost a 64-bit division per vector
   const long long total = m * vec_per_row;
+  const bool small = total <= 0x7fffffffLL;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; g < total; g += nthreads * UNROLL) {
@@ -29,7 +32,10 @@ __global__ void __launch_bounds__(256)
       const long long gu = g + (long long)u * nthreads;
       dst[u] = -1;
       if (gu < total) {
-        const long long row = gu / vec_per_row;
+        long long row;
+        if (row_shift >= 0) row = gu >> row_shift;
+        else if (small) row = (long long)((unsigned)gu / (unsigned)vec_per_row);
+        else row = gu / vec_per_row;
         const int col = (int)(gu - row * vec_per_row);
         long long src = (long long)idx[row];
         if (WRAP_NEGATIVE && src < 0) src += n_rows;

@@ -198,6 +198,17 @@ __device__ __forceinline__ auto igather(const T* p, const I& idx, const M& mask,
 }
 
 // ---- pointwise family -------------------------------------------------------------------
+// CTAs of `kern` that fit on the device at once.  Persistent kernels launch exactly this
+// many (or fewer, if the work is smaller): a grid of a few waves would leave the last wave
+// partly empty.
+template <class K> inline long long resident_ctas(K kern, int threads) {
+  int dev = 0, sms = 148, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, 0) != cudaSuccess || n < 1) n = 1;
+  return (long long)sms * n;
+}
+
 // true when every pointer argument of a generated module is 16-byte aligned
 inline bool pointers_aligned(void* const* ptrs, int n) {
   for (int i = 0; i < n; ++i)
@@ -219,12 +230,11 @@ __global__ void __launch_bounds__(256) pointwise_gen_kernel(const Body body, con
 }
 template <class Body> int launch_pointwise(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static const long long cap_a = resident_ctas(pointwise_gen_kernel<Body, true>, 256);
+  static const long long cap_u = resident_ctas(pointwise_gen_kernel<Body, false>, 256);
   const long long ntiles = (xnumel + Body::kVec - 1) / Body::kVec;
   long long grid = (ntiles + 255) / 256;
-  const long long cap = (long long)sms * 16;  // persistent beyond 16 CTAs per SM
+  const long long cap = aligned ? cap_a : cap_u;
   if (grid > cap) grid = cap;
   if (aligned) pointwise_gen_kernel<Body, true><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
   else pointwise_gen_kernel<Body, false><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
@@ -476,16 +486,23 @@ int launch_row_gen(const Body& body, long long rows, int cols, void* stream) {
 }
 
 // ---- outer reduction family -----------------------------------------------------------------
-// The kept (x) axis is stride-1 in memory and the reduced axis is not: threads map along x
-// (kVec consecutive elements each, a warp covers 32 * kVec of them) and the TY thread rows
-// of a CTA split the reduced axis; their partial vectors are folded through shared memory.
-// The generated body carries the loop over the reduced index itself:
-//   Body::tile(ctx, xbase, nvalid)  - for (r = ctx.ty; r < rnumel; r += kTY) {...}, then
-//                                     ctx.combine<Op>(acc), epilogue, stores by ty == 0.
+// The kept (x) axis is stride-1 in memory and the reduced axis is not.  Threads form a
+// TX x TY grid: TX threads cover the contiguous run of the kept axis (kVec elements each;
+// TX is chosen by the generator so that TX * kVec elements are adjacent in memory) and the
+// TY thread rows split the reduced axis.  With a short run a warp therefore reads 32 / TX
+// consecutive reduced indices, which are adjacent spans when the reduced stride equals the
+// run.  Partial vectors are folded by shuffles inside a warp and through shared memory
+// across warps.  The generated body carries the loop over the reduced index itself:
+//   Body::tile<FAST>(ctx, xbase, nvalid)  - for (r = ctx.ty; r < rnumel; r += kTY) {...},
+//                                           then ctx.combine<Op>(acc), epilogue, stores by
+//                                           the thread row ty == 0.
 template <int V, int TX, int TY> struct OuterCtx {
   static constexpr int kTY = TY;
+  static constexpr int kWarps = TX * TY / 32;
+  static constexpr int kRowsPerWarp = 32 / TX;   // thread rows that share a warp
+  static_assert(TX <= 32 && 32 % TX == 0 && (TX * TY) % 32 == 0, "thread grid must tile warps");
   int tx, ty;
-  float* part;  // [TY][TX * V]
+  float* part;  // [kWarps][TX * V]
 
   template <int N> static __device__ __forceinline__ vf<N> splat(float v) {
     vf<N> r;
@@ -495,18 +512,27 @@ template <int V, int TX, int TY> struct OuterCtx {
   }
   // fold the TY partial vectors; every thread row receives the result
   template <class Op> __device__ __forceinline__ vf<V> combine(const vf<V>& acc) {
+    vf<V> r = acc;
 #pragma unroll
-    for (int i = 0; i < V; ++i) part[(ty * TX + tx) * V + i] = acc.v[i];
-    __syncthreads();
-    vf<V> r;
+    for (int off = TX; off < 32; off <<= 1)
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      float a = part[tx * V + i];
+      for (int i = 0; i < V; ++i) r.v[i] = Op::combine(r.v[i], __shfl_xor_sync(kFull, r.v[i], off));
+    if constexpr (kWarps > 1) {
+      const int warp = (ty * TX + tx) >> 5;
+      if (ty % kRowsPerWarp == 0) {
 #pragma unroll
-      for (int y = 1; y < TY; ++y) a = Op::combine(a, part[(y * TX + tx) * V + i]);
-      r.v[i] = a;
+        for (int i = 0; i < V; ++i) part[(warp * TX + tx) * V + i] = r.v[i];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float a = part[tx * V + i];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) a = Op::combine(a, part[(w * TX + tx) * V + i]);
+        r.v[i] = a;
+      }
+      __syncthreads();
     }
-    __syncthreads();
     return r;
   }
 };
@@ -514,7 +540,7 @@ template <int V, int TX, int TY> struct OuterCtx {
 template <class Body, int TX, int TY, bool ALIGNED>
 __global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, const long long xnumel) {
   constexpr int V = Body::kVec;
-  __shared__ float part[TY * TX * V];
+  __shared__ __align__(16) float part[(TX * TY / 32) * TX * V];
   OuterCtx<V, TX, TY> c;
   c.tx = threadIdx.x % TX;
   c.ty = threadIdx.x / TX;
@@ -524,20 +550,20 @@ __global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, cons
   for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const long long xbase = t * per_cta + (long long)c.tx * V;
     const long long left = xnumel - xbase;
-    // the choice is uniform per warp only if whole CTAs take it: decided on the CTA's tile
+    // the choice is uniform per CTA (the fold synchronises the whole CTA)
     if (ALIGNED && xnumel - t * per_cta >= per_cta) body.template tile<true>(c, xbase, V);
     else body.template tile<false>(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
   }
 }
-template <class Body> int launch_outer_gen(const Body& body, long long xnumel, void* stream, bool aligned = false) {
+template <class Body, int TX = 32>
+int launch_outer_gen(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;
-  constexpr int TX = 32, TY = 8;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  constexpr int TY = 256 / TX;
+  static const long long cap_a = resident_ctas(outer_gen_kernel<Body, TX, TY, true>, TX * TY);
+  static const long long cap_u = resident_ctas(outer_gen_kernel<Body, TX, TY, false>, TX * TY);
   const long long per_cta = (long long)TX * Body::kVec;
   long long grid = (xnumel + per_cta - 1) / per_cta;
-  const long long cap = (long long)sms * 8;
+  const long long cap = aligned ? cap_a : cap_u;
   if (grid > cap) grid = cap;
   if (aligned) outer_gen_kernel<Body, TX, TY, true><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
   else outer_gen_kernel<Body, TX, TY, false><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);

@@ -85,7 +85,9 @@ def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backen
     x = torch.randn(4, 8, 16, 64).half()
     code = generated(lambda t: t.permute(0, 3, 1, 2).amax((2, 3)), x)
     assert code.count("ixb_load_kernel('''") == 1
-    assert "launch_outer_gen<Body>" in code and "family='outer'" in code
+    # 64 contiguous fp16 outputs = 8 vectors: 8 threads along the kept axis, the rest of
+    # each warp walks the reduced axis
+    assert "launch_outer_gen<Body, 8>" in code and "family='outer'" in code
     assert "c.template combine<ixb::MaxOp>(acc)" in code
     # an inner-axis reduction of the same tensor keeps the row mapping
     code = generated(lambda t: t.amax(-1), x)
