@@ -58,6 +58,16 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_bf16) 
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Development aid (never defined in the shipped build): CTA (0, 0) writes SM clock stamps
+// of its hand-offs into the buffer passed as `lse`.
+#ifdef IXB_FA_TIMING
+#define IXB_FA_STAMP(cond, slot)                                                       \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && (cond))                                    \
+    reinterpret_cast<long long*>(p.lse)[slot] = clock64();
+#else
+#define IXB_FA_STAMP(cond, slot)
+#endif
+
 template <bool IS_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -158,15 +168,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_pv = tc::instr_desc(BM, HD, IS_BF16 ? 1 : 0, 0, 1);
       // S_t = Q_t K_j^T: both operands K-major, 8 steps of 16 along the head dimension;
       // a step moves 32 bytes inside the 128-byte swizzled row, 4 steps per 64-column box
+      // Descriptors of the tile bases are formed once; a k-step only adds its byte offset
+      // (in 16-byte units) to the address field, which cannot carry out of it.
+      uint64_t q_desc[NQ], k_desc[kStages], v_desc[kStages];
+#pragma unroll
+      for (int t = 0; t < NQ; ++t) q_desc[t] = tc::smem_desc(smem_u32(q_smem + (size_t)t * kTileBytes), 16, 1024);
+#pragma unroll
+      for (int s = 0; s < kStages; ++s) {
+        k_desc[s] = tc::smem_desc(smem_u32(k_smem + (size_t)s * kTileBytes), 16, 1024);
+        v_desc[s] = tc::smem_desc(smem_u32(v_smem + (size_t)s * kTileBytes), kHalfBytes, 1024);
+      }
       auto issue_qk = [&](int t, int stage) {
-        const uint32_t q_addr = smem_u32(q_smem + (size_t)t * kTileBytes);
-        const uint32_t k_addr = smem_u32(k_smem + (size_t)stage * kTileBytes);
         const uint32_t d = tmem_base + kColS + t * 128;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-          tc::mma_ss(d, tc::smem_desc(q_addr + off, 16, 1024), tc::smem_desc(k_addr + off, 16, 1024),
-                     idesc_qk, ks > 0);
+          const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+          tc::mma_ss(d, q_desc[t] + off, k_desc[stage] + off, idesc_qk, ks > 0);
         }
       };
       // O_t += P_t V_j: A = P from TMEM (two 16-bit values per column, 8 columns per step),
@@ -175,15 +192,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       // box sits kHalfBytes further (leading-dimension offset); a step of 16 keys is two
       // atoms = 2048 bytes
       auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t v_addr = smem_u32(v_smem + (size_t)stage * kTileBytes);
         const uint32_t a = tmem_base + kColS + t * 128;
         const uint32_t d = tmem_base + kColO + t * 128;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          tc::mma_ts(d, a + ks * 8, tc::smem_desc(v_addr + ks * 2048, kHalfBytes, 1024), idesc_pv,
+          tc::mma_ts(d, a + ks * 8, v_desc[stage] + (uint32_t)(ks * 2048 >> 4), idesc_pv,
                      (accumulate || ks > 0) ? 1u : 0u);
         }
       };
+      int v_seen = -1, k_seen = 0;  // key tiles whose V / K arrival has been waited for
       bool ok = mbar_wait(&q_full, 0, &failed);
       if (ok && n_kv > 0) ok = mbar_wait(&k_full[0], 0, &failed);
       if (ok && n_kv > 0) {
@@ -202,23 +219,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int s1 = (j + 1) & 1, n1 = (j + 1) >> 1;
 #pragma unroll
         for (int t = 0; t < NQ; ++t) {
-          if (j < n_kv_t[t]) {
+          // every wait of this tile's step comes first, so that its sixteen MMAs go to the
+          // tensor core back to back and its queue does not drain in between
+          const bool do_pv = j < n_kv_t[t], do_qk = j + 1 < n_kv_t[t];
+          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 0);
+          if (do_pv) {
             ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
-            ok = ok && mbar_wait(&v_full[s], n & 1, &failed);
-            if (!ok) break;
-            tc::fence_after_sync();
+            if (v_seen != j) {  // a stage is waited for once, not once per tile
+              ok = ok && mbar_wait(&v_full[s], n & 1, &failed);
+              v_seen = j;
+            }
+          }
+          if (do_qk && k_seen != j + 1) {
+            ok = ok && mbar_wait(&k_full[s1], n1 & 1, &failed);
+            k_seen = j + 1;
+          }
+          if (!ok) break;
+          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 2);
+          tc::fence_after_sync();
+          if (do_pv) {
             issue_pv(t, s, j > 0);
             tc::mma_commit(&pv_done[t]);
           }
-          if (j + 1 < n_kv_t[t]) {
+          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 3);
+          if (do_qk) {
             // P_t(j) has been consumed by the MMAs just issued (the tensor core runs
             // them in order), so tile t's buffer can take S_t(j+1)
-            ok = ok && mbar_wait(&k_full[s1], n1 & 1, &failed);
-            if (!ok) break;
-            tc::fence_after_sync();
             issue_qk(t, s1);
             tc::mma_commit(&s_full[t]);
           }
+          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 5);
         }
         if (!ok) break;
         tc::mma_commit(&v_empty[s]);
@@ -248,6 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc::fence_after_sync();
+      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 0);
       const int col0 = j * BN;
       const bool edge = (col0 + BN > p.Sk) || (p.causal && (col0 + BN - 1 > qt0 + diag));
       // last visible key of this row, relative to the tile
@@ -275,6 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mx = max3(mx, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
         }
       }
+      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 1);
       mx *= p.scale_log2;  // scale > 0: scaling commutes with the maximum
       // lazy rescale: move the reference maximum only when it would grow by > 2^8
       const bool grow = mx > m_used + kRescaleThreshold;  // also true for the first tile
@@ -302,6 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         m_used = m_new;
       }
+      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 2);
       // ---- pass 2: P = exp2(s * scale - m_used); the next 32 columns are requested
       // before the current 32 are processed so the TMEM latency overlaps the arithmetic
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
@@ -337,6 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       l += sum2.x + sum2.y;
       tc::tmem_wait_st();
       tc::fence_before_sync();
+      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 3);
       tc::mbar_arrive(&p_full[t]);
     }
 
@@ -367,10 +401,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
+#ifndef IXB_FA_TIMING
         if (live && p.lse != nullptr) {
           const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.69314718055994530942f : -INFINITY;
           p.lse[((long long)b * p.H + h) * p.Sq + qi] = lse;
         }
+#endif
       }
     } else {
       failed = 1;

@@ -48,10 +48,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity,
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after about a second of SM clock (counter bumped), or as soon as
 // `abort` (a flag another role of the CTA raises when its own wait gave up) is non-zero.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           const volatile int* abort = nullptr) {
+  if (mbar_test_wait(bar, parity)) return true;  // already complete: the common case on a hot path
 #pragma unroll 1
   for (int quick = 0; quick < 64; ++quick)
     if (mbar_try_wait(bar, parity)) return true;
