@@ -468,10 +468,67 @@ class LlamaLayer:
         return fn, fl, f"{batch} x {seq} of {self.B} x {self.S} tokens, eager PyTorch bf16 on CPU"
 
 
+class CpMerge:
+    """Ring-attention merge step (the reference's forward_update profile case,
+    test/npu_indexing/written/test_attn_cp.py:241-252): (S, B, H, N) = (8192, 1, 6144, 48),
+    bf16 attention outputs, fp32 [B, N, S, 8] statistics."""
+
+    name = "cp_forward_update_bf16_s8192_h6144_n48"
+    dtype = "bf16"
+    S, B, H, N = 8192, 1, 6144, 48
+    KEYS = ("prev_attn_out", "prev_softmax_max", "prev_softmax_sum", "cur_attn_out", "cur_softmax_max",
+            "cur_softmax_sum")
+
+    def algorithmic_bytes(self):
+        attn = self.S * self.B * self.H * 2
+        stats = self.B * self.N * self.S * 8 * 4
+        return 3 * attn + 6 * stats   # two attention reads + one write; four statistics reads + two writes
+
+    def load_host(self, seed):
+        from oracle import inputs
+
+        self.host = inputs.cp_merge(self.S, self.B, self.H, self.N, seed=seed)
+        return self.host
+
+    def setup(self, device, seed, n_sets=2):
+        d = self.load_host(seed)
+        # two sets of ~240 MB of inputs each: more than L2 between consecutive steps
+        self.sets = [[d[k].to(device) for k in self.KEYS]]
+        for _ in range(n_sets - 1):
+            self.sets.append([t.clone() for t in self.sets[0]])
+
+    def step(self, i):
+        from inductor_x_b200 import ops
+
+        self.out = ops.forward_update(*self.sets[i % len(self.sets)])
+        return 1
+
+    def e2e_setup(self, device):
+        self.h_in = [self.host[k].pin_memory() for k in self.KEYS]
+        self.d_in = [torch.empty_like(t) for t in self.sets[0]]
+        self.h_o = torch.empty(self.S, self.B, self.H, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(self):
+        from inductor_x_b200 import ops
+
+        for d, h in zip(self.d_in, self.h_in):
+            d.copy_(h, non_blocking=True)
+        o, _, _ = ops.forward_update(*self.d_in)
+        self.h_o.copy_(o, non_blocking=True)
+        return sum(t.numel() * t.element_size() for t in self.h_in), self.h_o.numel() * 2
+
+    def cpu_sample(self):
+        from oracle import graphs
+
+        d = self.host
+        fn = lambda: graphs.cp_forward_update(**d)
+        return fn, self.algorithmic_bytes(), "full workload, eager PyTorch on CPU (the reference's forward_update)"
+
+
 WORKLOADS = {
     "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
     "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention,
-    "c5": LlamaLayer,
+    "c5": LlamaLayer, "cp": CpMerge,
 }
 
 

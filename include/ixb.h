@@ -232,6 +232,39 @@ int ixb_fa_fwd(int dtype, const void* q, const void* k, const void* v, void* o, 
                const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                float scale, int causal, int32_t* status, ixb_stream stream);
 
+/* ---- context-parallel attention merge ---------------------------------------------------- */
+
+/* Fold the partial attention result of one ring step into the running one, (max, sum) form:
+ *   m = max(pm, cm); ps = psum*exp(pm-m); cs = csum*exp(cm-m); l = ps+cs;
+ *   out_attn = prev_attn*(ps/l) + cur_attn*(cs/l); out_max = m; out_sum = l
+ * attn tensors [S, B, N*D] contiguous, dtype F32/F16/BF16 (fp32 math); statistics
+ * [B, N, S, 8] fp32 whose N axis has the given element stride (so a slice along S of a longer
+ * buffer can be passed), updated entry by entry; the attention weights use entry 0.
+ * D*elsize must be a multiple of 16 and all pointers 16-byte aligned.  Replaces the
+ * hand-written kernel tl_fn_forward_update
+ * (test/npu_indexing/written/attn_cp_triton_kernel_3d.py:15-82; eager form
+ * test/npu_indexing/attn_cp_test.py:36-59). */
+int ixb_cp_forward_update(int dtype, const void* prev_attn, const float* prev_max,
+                          const float* prev_sum, const void* cur_attn, const float* cur_max,
+                          const float* cur_sum, void* out_attn, float* out_max, float* out_sum,
+                          int32_t S, int32_t B, int32_t N, int32_t D, int64_t prev_stat_nstride,
+                          int64_t cur_stat_nstride, int64_t out_stat_nstride, ixb_stream stream);
+
+/* Log-sum-exp form, in place on the running result:
+ *   lse = log(exp(p)+exp(c)); prev_attn = exp(p-lse)*prev_attn + exp(c-lse)*cur_attn; prev_lse = lse
+ * attn [B, N, S, D] fp32 and lse [B, N, S] fp32, each with an element stride for its N axis;
+ * D a multiple of 4, attn pointers and strides 16-byte aligned.  Replaces
+ * tl_fn_forward_update_la (test/npu_indexing/written/attn_cp_triton_kernel_3d_la.py:11-55). */
+int ixb_cp_forward_update_lse(float* prev_attn, float* prev_lse, const float* cur_attn,
+                              const float* cur_lse, int32_t B, int32_t N, int32_t S, int32_t D,
+                              int64_t prev_attn_nstride, int64_t prev_lse_nstride,
+                              int64_t cur_attn_nstride, int64_t cur_lse_nstride, ixb_stream stream);
+
+/* acc += cur over numel contiguous elements (fp32 add, rounded to the storage type): the
+ * gradient accumulation of the ring backward (backward_update,
+ * test/npu_indexing/written/test_attn_cp.py:267-287).  numel*elsize a multiple of 16. */
+int ixb_cp_accumulate(int dtype, void* acc, const void* cur, int64_t numel, ixb_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

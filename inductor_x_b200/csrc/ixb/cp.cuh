@@ -1,0 +1,144 @@
+// Context-parallel attention merge kernels: fold the partial result of one ring step into
+// the running result.  They stand where the reference keeps hand-written Triton kernels
+//   tl_fn_forward_update     (test/npu_indexing/written/attn_cp_triton_kernel_3d.py:15-82)
+//   tl_fn_forward_update_la  (test/npu_indexing/written/attn_cp_triton_kernel_3d_la.py:11-55)
+// and the eager gradient accumulation of its ring backward
+//   backward_update          (test/npu_indexing/written/test_attn_cp.py:267-287).
+// All three are streaming kernels: every byte is read once and written once, 128 bits per
+// thread per access, persistent grids.
+#pragma once
+#include "common.cuh"
+
+namespace ixb {
+
+// ---- (max, sum) form ------------------------------------------------------------------
+// attn tensors are [S, B, H] (H = N * D, stride-1), statistics are [B, N, S, 8] fp32 with
+// the 8 entries of a row holding the same value (the layout of the vendor attention op);
+// `*_nstride` is the element stride of their N axis, so a slice along S of a longer buffer
+// can be passed as it is.  Per (s, b, n):
+//   m = max(pm, cm); ps = psum * exp(pm - m); cs = csum * exp(cm - m); l = ps + cs
+//   out = prev * (ps / l) + cur * (cs / l)          (fp32 math, stored in T)
+// The statistics are updated entry by entry, the attention scale uses entry 0
+// (attn_cp_test.py:24-33).
+template <typename T>
+__global__ void __launch_bounds__(256)
+    cp_forward_update_kernel(const T* __restrict__ prev_attn, const float* __restrict__ prev_max,
+                             const float* __restrict__ prev_sum, const T* __restrict__ cur_attn,
+                             const float* __restrict__ cur_max, const float* __restrict__ cur_sum,
+                             T* __restrict__ out_attn, float* __restrict__ out_max,
+                             float* __restrict__ out_sum, int S, int B, int N, int D,
+                             long long prev_nstride, long long cur_nstride, long long out_nstride) {
+  constexpr int kVec = Elem<T>::kVec;
+  const int H = N * D;
+  const int vec_per_row = H / kVec;      // vectors of one (s, b) row
+  const int vec_per_head = D / kVec;
+  const long long rows = (long long)S * B;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int s = (int)(row / B), b = (int)(row - (long long)s * B);
+    const T* pa = prev_attn + row * H;
+    const T* ca = cur_attn + row * H;
+    T* oa = out_attn + row * H;
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      const int n = v / vec_per_head;
+      const long long bn = (long long)b * N + n;
+      const long long po = bn * prev_nstride + (long long)s * 8;
+      const long long co = bn * cur_nstride + (long long)s * 8;
+      const float pm = prev_max[po], cm = cur_max[co];
+      const float m = fmaxf(pm, cm);
+      const float ps = prev_sum[po] * expf(pm - m);
+      const float cs = cur_sum[co] * expf(cm - m);
+      const float l = ps + cs;
+      const float wp = ps / l, wc = cs / l;
+      float a[kVec], c[kVec];
+      unpack<T>(ldg_stream(pa + (long long)v * kVec), a);
+      unpack<T>(ldg_stream(ca + (long long)v * kVec), c);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) a[i] = a[i] * wp + c[i] * wc;
+      stg_stream(oa + (long long)v * kVec, pack<T>(a));
+      if (v - n * vec_per_head == 0) {
+        // the head's first thread also writes the 8 statistics entries of (b, n, s)
+        const long long oo = bn * out_nstride + (long long)s * 8;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float4 pm4 = *reinterpret_cast<const float4*>(prev_max + po + q * 4);
+          const float4 cm4 = *reinterpret_cast<const float4*>(cur_max + co + q * 4);
+          const float4 ps4 = *reinterpret_cast<const float4*>(prev_sum + po + q * 4);
+          const float4 cs4 = *reinterpret_cast<const float4*>(cur_sum + co + q * 4);
+          float4 m4, l4;
+          m4.x = fmaxf(pm4.x, cm4.x);
+          m4.y = fmaxf(pm4.y, cm4.y);
+          m4.z = fmaxf(pm4.z, cm4.z);
+          m4.w = fmaxf(pm4.w, cm4.w);
+          l4.x = ps4.x * expf(pm4.x - m4.x) + cs4.x * expf(cm4.x - m4.x);
+          l4.y = ps4.y * expf(pm4.y - m4.y) + cs4.y * expf(cm4.y - m4.y);
+          l4.z = ps4.z * expf(pm4.z - m4.z) + cs4.z * expf(cm4.z - m4.z);
+          l4.w = ps4.w * expf(pm4.w - m4.w) + cs4.w * expf(cm4.w - m4.w);
+          *reinterpret_cast<float4*>(out_max + oo + q * 4) = m4;
+          *reinterpret_cast<float4*>(out_sum + oo + q * 4) = l4;
+        }
+      }
+    }
+  }
+}
+
+// ---- log-sum-exp form, in place ---------------------------------------------------------
+// attn tensors are [B, N, S, D] fp32 (D stride-1, `*_attn_nstride` = element stride of N),
+// lse tensors [B, N, S] fp32.  Per (b, n, s):
+//   lse = log(exp(p) + exp(c)); prev_attn = exp(p - lse) * prev_attn + exp(c - lse) * cur_attn
+//   prev_lse = lse
+// The sum of exponentials is taken relative to max(p, c), which is the same value without
+// the overflow of the literal form.
+__global__ void __launch_bounds__(256)
+    cp_forward_update_lse_kernel(float* __restrict__ prev_attn, float* __restrict__ prev_lse,
+                                 const float* __restrict__ cur_attn, const float* __restrict__ cur_lse,
+                                 int BN, int S, int D, long long prev_attn_nstride,
+                                 long long prev_lse_nstride, long long cur_attn_nstride,
+                                 long long cur_lse_nstride) {
+  // one warp per (b, n, s) row: every lane reads the row's old lse before lane 0 replaces it
+  const int vec_per_row = D / 4;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)BN * S;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const long long bn = r / S;
+    const int s = (int)(r - bn * S);
+    float* lse_slot = prev_lse + bn * prev_lse_nstride + s;
+    const float p = *lse_slot;
+    const float c = cur_lse[bn * cur_lse_nstride + s];
+    __syncwarp();
+    const float m = fmaxf(p, c);
+    const float lse = (m == -INFINITY) ? -INFINITY : m + logf(expf(p - m) + expf(c - m));
+    const float wp = (lse == -INFINITY) ? 0.f : expf(p - lse);
+    const float wc = (lse == -INFINITY) ? 0.f : expf(c - lse);
+    float* pa = prev_attn + bn * prev_attn_nstride + (long long)s * D;
+    const float* ca = cur_attn + bn * cur_attn_nstride + (long long)s * D;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      float4 a = *reinterpret_cast<const float4*>(pa + v * 4);
+      const uint4 craw = ldg_stream(ca + v * 4);
+      a.x = wp * a.x + wc * __uint_as_float(craw.x);
+      a.y = wp * a.y + wc * __uint_as_float(craw.y);
+      a.z = wp * a.z + wc * __uint_as_float(craw.z);
+      a.w = wp * a.w + wc * __uint_as_float(craw.w);
+      *reinterpret_cast<float4*>(pa + v * 4) = a;
+    }
+    if (lane == 0) *lse_slot = lse;
+  }
+}
+
+// ---- gradient accumulation: acc += cur, fp32 add, rounded to T (torch's add_ on 16-bit) ---
+template <typename T>
+__global__ void __launch_bounds__(256)
+    accumulate_kernel(T* __restrict__ acc, const T* __restrict__ cur, long long nvec) {
+  constexpr int kVec = Elem<T>::kVec;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < nvec; g += stride) {
+    float a[kVec], c[kVec];
+    unpack<T>(*reinterpret_cast<const uint4*>(acc + g * kVec), a);
+    unpack<T>(ldg_stream(cur + g * kVec), c);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) a[i] += c[i];
+    *reinterpret_cast<uint4*>(acc + g * kVec) = pack<T>(a);
+  }
+}
+
+}  // namespace ixb

@@ -218,3 +218,84 @@ def fused_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
     if status is not None and int(status.item()) != 0:
         raise RuntimeError("ixb_fa_fwd: an internal pipeline wait gave up; output is undefined")
     return (out, lse) if return_lse else out
+
+
+# ---- context-parallel attention merge ----------------------------------------------------
+def _stat_nstride(t: torch.Tensor, S: int) -> int:
+    """Element stride of the N axis of a ``[B, N, S, 8]`` statistics tensor whose last two
+    axes are dense and whose B axis is ``N`` times the N stride (a slice along S of a longer
+    buffer qualifies)."""
+    B, N = t.shape[0], t.shape[1]
+    if t.stride(3) != 1 or t.stride(2) != 8 or (B > 1 and t.stride(0) != N * t.stride(1)):
+        raise ValueError("statistics must be [B, N, S, 8] with dense trailing axes")
+    return t.stride(1) if N > 1 else S * 8
+
+
+def forward_update(prev_attn_out: torch.Tensor, prev_softmax_max: torch.Tensor,
+                   prev_softmax_sum: torch.Tensor, cur_attn_out: torch.Tensor,
+                   cur_softmax_max: torch.Tensor, cur_softmax_sum: torch.Tensor):
+    """Merge the attention result of one ring step into the running result, (max, sum) form.
+    Same name, arguments and return value ``(attn_out, softmax_max, softmax_sum)`` as the
+    reference's ``forward_update`` / ``forward_update_triton``
+    (``test/npu_indexing/attn_cp_test.py:36-59``,
+    ``test/npu_indexing/written/attn_cp_triton_kernel_3d.py:85-140``): attention outputs are
+    ``[S, B, H]``, statistics ``[B, N, S, 8]`` fp32."""
+    _need_cuda(prev_attn_out, prev_softmax_max, prev_softmax_sum, cur_attn_out, cur_softmax_max, cur_softmax_sum)
+    S, B, H = cur_attn_out.shape
+    N = cur_softmax_max.shape[1]
+    if prev_attn_out.shape != cur_attn_out.shape or prev_attn_out.dtype != cur_attn_out.dtype:
+        raise ValueError("prev and cur attention outputs must share shape and dtype")
+    if H % N != 0:
+        raise ValueError("hidden size must be a multiple of the number of heads")
+    for t in (prev_softmax_max, prev_softmax_sum, cur_softmax_max, cur_softmax_sum):
+        if t.dtype != torch.float32 or tuple(t.shape) != (B, N, S, 8):
+            raise ValueError("statistics must be fp32 [B, N, S, 8]")
+    if not (prev_attn_out.is_contiguous() and cur_attn_out.is_contiguous()):
+        raise ValueError("attention outputs must be contiguous [S, B, H]")
+    pns, cns = _stat_nstride(prev_softmax_max, S), _stat_nstride(cur_softmax_max, S)
+    if _stat_nstride(prev_softmax_sum, S) != pns or _stat_nstride(cur_softmax_sum, S) != cns:
+        raise ValueError("max and sum of one side must share their layout")
+    attn_out = torch.empty_like(cur_attn_out)
+    out_max = torch.empty((B, N, S, 8), dtype=torch.float32, device=cur_attn_out.device)
+    out_sum = torch.empty_like(out_max)
+    rt.check("ixb_cp_forward_update", rt.load().ixb_cp_forward_update(
+        rt.DTYPE_CODE[cur_attn_out.dtype], prev_attn_out.data_ptr(), prev_softmax_max.data_ptr(),
+        prev_softmax_sum.data_ptr(), cur_attn_out.data_ptr(), cur_softmax_max.data_ptr(),
+        cur_softmax_sum.data_ptr(), attn_out.data_ptr(), out_max.data_ptr(), out_sum.data_ptr(),
+        S, B, N, H // N, pns, cns, S * 8, rt.raw_stream(cur_attn_out.device)))
+    return attn_out, out_max, out_sum
+
+
+def forward_update_la(prev_attn_out: torch.Tensor, prev_softmax_log_max_sum: torch.Tensor,
+                      cur_attn_out: torch.Tensor, cur_softmax_log_max_sum: torch.Tensor) -> None:
+    """Log-sum-exp form of the ring merge, in place on ``prev_attn_out`` ``[B, N, S, D]`` fp32
+    and ``prev_softmax_log_max_sum`` ``[B, N, S]`` fp32 (the reference's
+    ``forward_update_triton`` of ``test/npu_indexing/written/attn_cp_triton_kernel_3d_la.py:58-96``)."""
+    _need_cuda(prev_attn_out, prev_softmax_log_max_sum, cur_attn_out, cur_softmax_log_max_sum)
+    B, N, S, D = cur_attn_out.shape
+    for a in (prev_attn_out, cur_attn_out):
+        if a.dtype != torch.float32 or tuple(a.shape) != (B, N, S, D) or a.stride(3) != 1 or a.stride(2) != D \
+                or (B > 1 and a.stride(0) != N * a.stride(1)):
+            raise ValueError("attention outputs must be fp32 [B, N, S, D] with dense trailing axes")
+    for l in (prev_softmax_log_max_sum, cur_softmax_log_max_sum):
+        if l.dtype != torch.float32 or tuple(l.shape) != (B, N, S) or l.stride(2) != 1 \
+                or (B > 1 and l.stride(0) != N * l.stride(1)):
+            raise ValueError("log-sum-exp tensors must be fp32 [B, N, S] with a dense S axis")
+    ns = lambda t, dense: t.stride(1) if N > 1 else dense
+    rt.check("ixb_cp_forward_update_lse", rt.load().ixb_cp_forward_update_lse(
+        prev_attn_out.data_ptr(), prev_softmax_log_max_sum.data_ptr(), cur_attn_out.data_ptr(),
+        cur_softmax_log_max_sum.data_ptr(), B, N, S, D, ns(prev_attn_out, S * D),
+        ns(prev_softmax_log_max_sum, S), ns(cur_attn_out, S * D), ns(cur_softmax_log_max_sum, S),
+        rt.raw_stream(cur_attn_out.device)))
+
+
+def grad_accumulate(acc: torch.Tensor, cur: torch.Tensor) -> torch.Tensor:
+    """``acc.add_(cur.view(acc.shape))`` for dense tensors: the gradient accumulation steps of
+    the reference's ring backward (``backward_update``,
+    ``test/npu_indexing/written/test_attn_cp.py:267-287``)."""
+    _need_cuda(acc, cur)
+    if acc.dtype != cur.dtype or acc.numel() != cur.numel() or not (acc.is_contiguous() and cur.is_contiguous()):
+        raise ValueError("acc and cur must be dense tensors of one dtype and size")
+    rt.check("ixb_cp_accumulate", rt.load().ixb_cp_accumulate(
+        rt.DTYPE_CODE[acc.dtype], acc.data_ptr(), cur.data_ptr(), acc.numel(), rt.raw_stream(acc.device)))
+    return acc

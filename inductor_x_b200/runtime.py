@@ -106,6 +106,9 @@ _SIGNATURES = {
                            POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_void_p, c_void_p]),
     "ixb_index_select_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                       c_int, c_int, c_void_p, c_void_p]),
+    "ixb_cp_forward_update": (c_int, [c_int] + [c_void_p] * 9 + [c_int32] * 4 + [c_int64] * 3 + [c_void_p]),
+    "ixb_cp_forward_update_lse": (c_int, [c_void_p] * 4 + [c_int32] * 4 + [c_int64] * 4 + [c_void_p]),
+    "ixb_cp_accumulate": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p]),
 }
 
 _lib: Optional[ctypes.CDLL] = None

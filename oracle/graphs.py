@@ -160,3 +160,34 @@ def max_rel_err(actual, expected, floor=None, dim=None):
             floor = e.pow(2).mean(dim, keepdim=True).sqrt().clamp_min(1e-30)
             return float(((a - e).abs() / torch.maximum(e.abs(), floor)).max())
     return float(((a - e).abs() / e.abs().clamp_min(floor)).max())
+
+
+# ---- context-parallel attention merge (ring step) ----------------------------------------
+def cp_forward_update(prev_attn_out, prev_softmax_max, prev_softmax_sum, cur_attn_out, cur_softmax_max,
+                      cur_softmax_sum):
+    """Eager (max, sum) merge, as the reference states it
+    (test/npu_indexing/attn_cp_test.py:24-59): statistics [B, N, S, 8], attention outputs
+    [S, B, H]; the scale of an output element comes from entry 0 of its (b, n, s) row."""
+    org_dtype = prev_attn_out.dtype
+    softmax_max = torch.maximum(prev_softmax_max, cur_softmax_max)
+    prev_scaled = prev_softmax_sum * torch.exp(prev_softmax_max - softmax_max)
+    cur_scaled = cur_softmax_sum * torch.exp(cur_softmax_max - softmax_max)
+    softmax_sum = prev_scaled + cur_scaled
+
+    def to_sbh(x):  # [B, N, S, 8] -> [S, B, N*D]
+        b, n, s, _ = x.shape
+        d = prev_attn_out.shape[-1] // n
+        return x[..., 0].unsqueeze(3).expand(b, n, s, d).permute(2, 0, 1, 3).reshape(s, b, n * d)
+
+    attn = prev_attn_out.float() * to_sbh(prev_scaled / softmax_sum) + \
+        cur_attn_out.float() * to_sbh(cur_scaled / softmax_sum)
+    return attn.to(org_dtype), softmax_max, softmax_sum
+
+
+def cp_forward_update_la(prev_attn_out, prev_lse, cur_attn_out, cur_lse):
+    """Eager log-sum-exp merge; returns the new (attn_out, lse) instead of updating in place
+    (test/npu_indexing/written/attn_cp_triton_kernel_3d_la.py:43-55)."""
+    lse = torch.logaddexp(prev_lse.double(), cur_lse.double())
+    attn = torch.exp(prev_lse.double() - lse).unsqueeze(-1) * prev_attn_out.double() + \
+        torch.exp(cur_lse.double() - lse).unsqueeze(-1) * cur_attn_out.double()
+    return attn.float(), lse.float()

@@ -102,3 +102,20 @@ def rope_tables(seq: int, head_dim: int, theta: float = 1e4):
     ang = torch.outer(torch.arange(seq, dtype=torch.float32), inv)
     ang = torch.cat([ang, ang], dim=-1)
     return ang.cos(), ang.sin()
+
+
+def cp_merge(S: int = 8192, B: int = 1, H: int = 6144, N: int = 48, seed: int = 7, dtype=torch.bfloat16):
+    """Inputs of one ring-attention merge step with the shapes of the reference's own
+    profile case ((S, B, H, N) = (4096, 1, 6144, 48) over a doubled sequence,
+    test/npu_indexing/written/test_attn_cp.py:241-252): attention outputs [S, B, H],
+    statistics [B, N, S, 8] with the eight entries of a row equal."""
+    g = _gen(seed)
+    rep = lambda t: t.unsqueeze(3).repeat(1, 1, 1, 8)
+    return {
+        "prev_attn_out": torch.randn((S, B, H), generator=g).to(dtype),
+        "prev_softmax_max": rep(torch.rand((B, N, S), generator=g)),
+        "prev_softmax_sum": rep(torch.rand((B, N, S), generator=g) + 0.5),
+        "cur_attn_out": torch.randn((S, B, H), generator=g).to(dtype),
+        "cur_softmax_max": rep(torch.rand((B, N, S), generator=g)),
+        "cur_softmax_sum": rep(torch.rand((B, N, S), generator=g) + 0.5),
+    }

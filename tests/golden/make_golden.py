@@ -92,5 +92,25 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_cp():
+    """Fixtures of the context-parallel merge kernels (a file of their own so that adding
+    them did not rewrite the fixtures above): complete outputs of a small (max, sum) merge
+    with statistics sliced out of a longer buffer, and of a small log-sum-exp merge."""
+    g = {"torch_version": str(torch.__version__)}
+    d = inputs.cp_merge(S=48, B=2, H=256, N=2, seed=21)
+    g["cp_small"] = [t.clone() for t in graphs.cp_forward_update(**d)]
+    gen = torch.Generator().manual_seed(22)
+    pa, ca = torch.randn((2, 3, 40, 64), generator=gen), torch.randn((2, 3, 40, 64), generator=gen)
+    pl, cl = torch.randn((2, 3, 40), generator=gen) * 3, torch.randn((2, 3, 40), generator=gen) * 3
+    g["cp_la_inputs"] = [pa, pl, ca, cl]
+    g["cp_la_small"] = list(graphs.cp_forward_update_la(pa, pl, ca, cl))
+    path = os.path.join(ROOT, "tests", "golden", "golden_cp.pt")
+    torch.save(g, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "cp":
+        main_cp()
+        sys.exit(0)
     main()

@@ -100,3 +100,50 @@ def test_llama_layer_runs_small():
     x = inputs.c5_input(2, 16, 64, seed=1)
     y = graphs.llama_layer(x, w, heads=4)
     assert y.shape == x.shape and torch.isfinite(y.float()).all()
+
+
+# ---- context-parallel merge -----------------------------------------------------------------
+def _cp_golden():
+    import os
+    return torch.load(os.path.join(os.path.dirname(__file__), "golden", "golden_cp.pt"), weights_only=True)
+
+
+def test_cp_forward_update_matches_golden_and_scalar_restatement():
+    """Eager merge against the committed fixture and against a scalar loop that follows the
+    hand-written kernel's index arithmetic (attn_cp_triton_kernel_3d.py:36-82)."""
+    import math
+    g = _cp_golden()
+    d = inputs.cp_merge(S=48, B=2, H=256, N=2, seed=21)
+    out, mx, sm = graphs.cp_forward_update(**d)
+    assert torch.equal(out, g["cp_small"][0]) and torch.equal(mx, g["cp_small"][1])
+    assert torch.allclose(sm, g["cp_small"][2], rtol=1e-6, atol=0)
+    S, B, H = d["cur_attn_out"].shape
+    N = 2
+    D = H // N
+    for (s, b, h) in [(0, 0, 0), (47, 1, 255), (13, 0, 128), (30, 1, 127)]:
+        n = h // D
+        pm, cm = float(d["prev_softmax_max"][b, n, s, 0]), float(d["cur_softmax_max"][b, n, s, 0])
+        m = max(pm, cm)
+        ps = float(d["prev_softmax_sum"][b, n, s, 0]) * math.exp(pm - m)
+        cs = float(d["cur_softmax_sum"][b, n, s, 0]) * math.exp(cm - m)
+        want = float(d["prev_attn_out"][s, b, h]) * ps / (ps + cs) + float(d["cur_attn_out"][s, b, h]) * cs / (ps + cs)
+        assert abs(float(out[s, b, h]) - want) <= 2e-2 * max(1.0, abs(want))
+        assert abs(float(sm[b, n, s, 3]) - (ps + cs)) <= 1e-5
+
+
+def test_cp_lse_form_agrees_with_max_sum_form():
+    """lse = max + log(sum): merging in the log-sum-exp form must give the same attention
+    output as merging (max, sum) pairs."""
+    g = _cp_golden()
+    pa, pl, ca, cl = g["cp_la_inputs"]
+    attn, lse = graphs.cp_forward_update_la(pa, pl, ca, cl)
+    assert torch.allclose(attn, g["cp_la_small"][0], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(lse, g["cp_la_small"][1], rtol=1e-6, atol=1e-6)
+    # the same step written with (max, sum): choose max = lse, sum = 1
+    B, N, S, D = pa.shape
+    rep = lambda t: t.unsqueeze(3).repeat(1, 1, 1, 8)
+    sbh = lambda t: t.permute(2, 0, 1, 3).reshape(S, B, N * D)
+    out, mx, sm = graphs.cp_forward_update(sbh(pa), rep(pl), rep(torch.ones_like(pl)), sbh(ca), rep(cl),
+                                           rep(torch.ones_like(cl)))
+    assert torch.allclose(out, sbh(attn), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(mx[..., 0] + torch.log(sm[..., 0]), lse, rtol=1e-5, atol=1e-5)
