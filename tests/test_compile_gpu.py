@@ -236,3 +236,18 @@ def test_context_parallel_softmax_merge(cuda):
     outs, _ = compile_and_code(forward_update, prev_out, prev_max, prev_sum, cur_out, cur_max, cur_sum)
     for a, e in zip(outs, forward_update(prev_out, prev_max, prev_sum, cur_out, cur_max, cur_sum)):
         torch.testing.assert_close(a, e, rtol=1e-5, atol=1e-5)
+
+
+def test_accuracy_check_walks_every_intermediate_of_config_2():
+    """The per-intermediate harness on the softmax -> LayerNorm chain: every node Dynamo
+    captured is produced by the generated kernels (all intermediates are graph outputs) and
+    agrees with eager within the 16-bit tolerance."""
+    from inductor_x_b200 import accuracy_check as ac
+
+    d = inputs.c2(64, 4096, seed=3)
+    x, g, ga, be = (d[k].cuda() for k in ("x", "g", "gamma", "beta"))
+    rep = ac.check(lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5),
+                   x, g, ga, be)
+    assert len(rep.records) >= 4, rep.format()
+    assert rep.ok, rep.format()
+    assert all(r.compiled_md5 is not None for r in rep.records)
