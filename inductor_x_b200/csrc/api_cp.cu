@@ -17,7 +17,7 @@ int forward_update_t(const void* prev_attn, const float* prev_max, const float* 
                      float* out_max, float* out_sum, int S, int B, int N, int D, int64_t prev_ns,
                      int64_t cur_ns, int64_t out_ns, const ixb_devinfo* dev, cudaStream_t s) {
   auto kern = ixb::cp_forward_update_kernel<T>;
-  long long grid = (long long)S * B;
+  long long grid = ((long long)S * B + 1) / 2;  // two rows per CTA iteration
   const long long cap = resident(kern, dev);
   if (grid > cap) grid = cap;
   kern<<<(unsigned)grid, 256, 0, s>>>((const T*)prev_attn, prev_max, prev_sum, (const T*)cur_attn, cur_max,

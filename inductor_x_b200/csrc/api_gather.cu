@@ -25,7 +25,7 @@ int gather_t(const void* table, const void* idx, void* out, int64_t n_rows, int6
       for (shift = 0; (1 << shift) < vpr; ++shift) {}
     // Persistent launch: exactly the CTAs that are resident at once, each striding over the
     // vectors.  A grid of a few waves would leave the last wave partly empty.
-    constexpr int kUnroll = 1;
+    constexpr int kUnroll = 2;
     auto kern = ixb::gather_rows_kernel<IdxT, kUnroll, WRAP>;
     static int resident[64] = {};
     int devid = 0;
