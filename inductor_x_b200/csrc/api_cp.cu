@@ -17,12 +17,20 @@ int forward_update_t(const void* prev_attn, const float* prev_max, const float* 
                      float* out_max, float* out_sum, int S, int B, int N, int D, int64_t prev_ns,
                      int64_t cur_ns, int64_t out_ns, const ixb_devinfo* dev, cudaStream_t s) {
   auto kern = ixb::cp_forward_update_kernel<T>;
-  long long grid = ((long long)S * B + 1) / 2;  // two rows per CTA iteration
-  const long long cap = resident(kern, dev);
+  const size_t smem = (size_t)2 * N * sizeof(float2);   // weights of two rows in flight
+  if (smem > 48 * 1024) return IXB_ERR_SHAPE;
+  const int vph = D / ixb::Elem<T>::kVec;
+  int shift = -1;
+  if ((vph & (vph - 1)) == 0)
+    for (shift = 0; (1 << shift) < vph; ++shift) {}
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
+  long long grid = (long long)S * B;
+  const long long cap = (long long)dev->sm_count * n;
   if (grid > cap) grid = cap;
-  kern<<<(unsigned)grid, 256, 0, s>>>((const T*)prev_attn, prev_max, prev_sum, (const T*)cur_attn, cur_max,
-                                     cur_sum, (T*)out_attn, out_max, out_sum, S, B, N, D, prev_ns, cur_ns,
-                                     out_ns);
+  kern<<<(unsigned)grid, 256, smem, s>>>((const T*)prev_attn, prev_max, prev_sum, (const T*)cur_attn, cur_max,
+                                        cur_sum, (T*)out_attn, out_max, out_sum, S, B, N, D, prev_ns, cur_ns,
+                                        out_ns, shift);
   return ixb_host::cuda_status(cudaGetLastError());
 }
 

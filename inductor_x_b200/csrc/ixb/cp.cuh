@@ -20,6 +20,11 @@ namespace ixb {
 //   out = prev * (ps / l) + cur * (cs / l)          (fp32 math, stored in T)
 // The statistics are updated entry by entry, the attention scale uses entry 0
 // (attn_cp_test.py:24-33).
+// A CTA walks (s, b) rows of the attention tensors.  Per row, one thread per head first
+// merges that head's statistics (all eight entries, written out) and leaves the two
+// attention weights in shared memory; then the whole CTA streams the row, 128 bits per
+// access, looking its weights up by head.  The weight buffers alternate between rows, so one
+// barrier per row is enough.
 template <typename T>
 __global__ void __launch_bounds__(256)
     cp_forward_update_kernel(const T* __restrict__ prev_attn, const float* __restrict__ prev_max,
@@ -27,75 +32,58 @@ __global__ void __launch_bounds__(256)
                              const float* __restrict__ cur_max, const float* __restrict__ cur_sum,
                              T* __restrict__ out_attn, float* __restrict__ out_max,
                              float* __restrict__ out_sum, int S, int B, int N, int D,
-                             long long prev_nstride, long long cur_nstride, long long out_nstride) {
+                             long long prev_nstride, long long cur_nstride, long long out_nstride,
+                             int head_shift) {
+  extern __shared__ float2 cp_weights[];   // [2][N]
   constexpr int kVec = Elem<T>::kVec;
-  constexpr int U = 2;                   // rows in flight per thread: their loads go out together
   const int H = N * D;
-  const int vec_per_row = H / kVec;      // vectors of one (s, b) row
-  const int vec_per_head = D / kVec;
+  const int vec_per_row = H / kVec;
+  const int vph = D / kVec;              // vectors of one head; head_shift = log2(vph) or -1
   const long long rows = (long long)S * B;
-  for (long long row0 = blockIdx.x; row0 < rows; row0 += (long long)gridDim.x * U) {
+  int parity = 0;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+    const int s = (int)(row / B), b = (int)(row - (long long)s * B);
+    float2* w = cp_weights + parity * N;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      const long long bn = (long long)b * N + n;
+      const long long po = bn * prev_nstride + (long long)s * 8;
+      const long long co = bn * cur_nstride + (long long)s * 8;
+      const long long oo = bn * out_nstride + (long long)s * 8;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const float4 pm4 = *reinterpret_cast<const float4*>(prev_max + po + q * 4);
+        const float4 cm4 = *reinterpret_cast<const float4*>(cur_max + co + q * 4);
+        const float4 ps4 = *reinterpret_cast<const float4*>(prev_sum + po + q * 4);
+        const float4 cs4 = *reinterpret_cast<const float4*>(cur_sum + co + q * 4);
+        float4 m4, l4;
+        m4.x = fmaxf(pm4.x, cm4.x);
+        m4.y = fmaxf(pm4.y, cm4.y);
+        m4.z = fmaxf(pm4.z, cm4.z);
+        m4.w = fmaxf(pm4.w, cm4.w);
+        const float psx = ps4.x * expf(pm4.x - m4.x), csx = cs4.x * expf(cm4.x - m4.x);
+        l4.x = psx + csx;
+        l4.y = ps4.y * expf(pm4.y - m4.y) + cs4.y * expf(cm4.y - m4.y);
+        l4.z = ps4.z * expf(pm4.z - m4.z) + cs4.z * expf(cm4.z - m4.z);
+        l4.w = ps4.w * expf(pm4.w - m4.w) + cs4.w * expf(cm4.w - m4.w);
+        *reinterpret_cast<float4*>(out_max + oo + q * 4) = m4;
+        *reinterpret_cast<float4*>(out_sum + oo + q * 4) = l4;
+        if (q == 0) w[n] = make_float2(psx / l4.x, csx / l4.x);   // entry 0 scales the output
+      }
+    }
+    __syncthreads();
+    const T* pa = prev_attn + row * H;
+    const T* ca = cur_attn + row * H;
+    T* oa = out_attn + row * H;
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-      const int n = v / vec_per_head;
-      uint4 praw[U], craw[U];
-      float pm[U], cm[U], psum[U], csum[U];
-      long long po[U], co[U];
-      int s_[U], b_[U];
+      const uint4 praw = ldg_stream(pa + (long long)v * kVec);
+      const uint4 craw = ldg_stream(ca + (long long)v * kVec);
+      const float2 ww = w[head_shift >= 0 ? (v >> head_shift) : (v / vph)];
+      float a[kVec], c[kVec];
+      unpack<T>(praw, a);
+      unpack<T>(craw, c);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long row = row0 + (long long)u * gridDim.x;
-        if (row < rows) {
-          s_[u] = (int)(row / B);
-          b_[u] = (int)(row - (long long)s_[u] * B);
-          const long long bn = (long long)b_[u] * N + n;
-          po[u] = bn * prev_nstride + (long long)s_[u] * 8;
-          co[u] = bn * cur_nstride + (long long)s_[u] * 8;
-          praw[u] = ldg_stream(prev_attn + row * H + (long long)v * kVec);
-          craw[u] = ldg_stream(cur_attn + row * H + (long long)v * kVec);
-          pm[u] = prev_max[po[u]];
-          cm[u] = cur_max[co[u]];
-          psum[u] = prev_sum[po[u]];
-          csum[u] = cur_sum[co[u]];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long row = row0 + (long long)u * gridDim.x;
-        if (row >= rows) continue;
-        const float m = fmaxf(pm[u], cm[u]);
-        const float ps = psum[u] * expf(pm[u] - m);
-        const float cs = csum[u] * expf(cm[u] - m);
-        const float l = ps + cs;
-        const float wp = ps / l, wc = cs / l;
-        float a[kVec], c[kVec];
-        unpack<T>(praw[u], a);
-        unpack<T>(craw[u], c);
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) a[i] = a[i] * wp + c[i] * wc;
-        stg_stream(out_attn + row * H + (long long)v * kVec, pack<T>(a));
-        if (v - n * vec_per_head == 0) {
-          // the head's first thread also writes the 8 statistics entries of (b, n, s)
-          const long long oo = ((long long)b_[u] * N + n) * out_nstride + (long long)s_[u] * 8;
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const float4 pm4 = *reinterpret_cast<const float4*>(prev_max + po[u] + q * 4);
-            const float4 cm4 = *reinterpret_cast<const float4*>(cur_max + co[u] + q * 4);
-            const float4 ps4 = *reinterpret_cast<const float4*>(prev_sum + po[u] + q * 4);
-            const float4 cs4 = *reinterpret_cast<const float4*>(cur_sum + co[u] + q * 4);
-            float4 m4, l4;
-            m4.x = fmaxf(pm4.x, cm4.x);
-            m4.y = fmaxf(pm4.y, cm4.y);
-            m4.z = fmaxf(pm4.z, cm4.z);
-            m4.w = fmaxf(pm4.w, cm4.w);
-            l4.x = ps4.x * expf(pm4.x - m4.x) + cs4.x * expf(cm4.x - m4.x);
-            l4.y = ps4.y * expf(pm4.y - m4.y) + cs4.y * expf(cm4.y - m4.y);
-            l4.z = ps4.z * expf(pm4.z - m4.z) + cs4.z * expf(cm4.z - m4.z);
-            l4.w = ps4.w * expf(pm4.w - m4.w) + cs4.w * expf(cm4.w - m4.w);
-            *reinterpret_cast<float4*>(out_max + oo + q * 4) = m4;
-            *reinterpret_cast<float4*>(out_sum + oo + q * 4) = l4;
-          }
-        }
-      }
+      for (int i = 0; i < kVec; ++i) a[i] = a[i] * ww.x + c[i] * ww.y;
+      stg_stream(oa + (long long)v * kVec, pack<T>(a));
     }
   }
 }
