@@ -251,3 +251,45 @@ def test_accuracy_check_walks_every_intermediate_of_config_2():
     assert len(rep.records) >= 4, rep.format()
     assert rep.ok, rep.format()
     assert all(r.compiled_md5 is not None for r in rep.records)
+
+
+def _top2_gating(logits, capacity: int):
+    """Top-2 expert gating in the style of the reference's MoE workload
+    (test/npu_indexing/moe/run_moe.py:24-112): softmax over experts, top-2 choice, one-hot
+    masks, running positions inside each expert's capacity buffer (cumsum), capacity cut,
+    renormalised gate weights and flattened (expert, slot) indices."""
+    probs = torch.softmax(logits, dim=1)
+    n_exp = probs.shape[1]
+    _, chosen = torch.topk(probs, 2, dim=-1)
+    mask = F.one_hot(chosen, num_classes=n_exp)
+    first, second = mask[:, 0, :], mask[:, 1, :]
+    pos1 = torch.cumsum(first, dim=0) - 1
+    pos2 = torch.cumsum(second, dim=0) - 1 + torch.sum(first, dim=0, keepdim=True)
+    aux = torch.mean(probs, dim=0) * torch.mean(first.float(), dim=0)
+    l_aux = aux.sum() * n_exp
+    first = first * torch.lt(pos1, capacity)
+    second = second * torch.lt(pos2, capacity)
+    slot1 = torch.sum(pos1 * first, dim=1)
+    slot2 = torch.sum(pos2 * second, dim=1)
+    w1, e1 = torch.max(probs * first.float(), dim=1)
+    w2, e2 = torch.max(probs * second.float(), dim=1)
+    denom = torch.clamp(w1 + w2, min=torch.finfo(probs.dtype).eps)
+    flat = torch.cat([e1.int() * capacity + slot1.int(), e2.int() * capacity + slot2.int()], dim=0)
+    weights = torch.cat([w1 / denom, w2 / denom], dim=0)
+    return l_aux, flat, weights
+
+
+@pytest.mark.parametrize("tokens,experts", [(4096, 16), (1000, 8)])
+def test_moe_top2_gating_graph(tokens, experts):
+    """Scan / top-k stay extern kernels, everything between them (softmax, one-hot masks,
+    integer sums along both axes, max with index, clamp, integer index arithmetic, cat) is
+    generated.  Integer outputs must be exact, float outputs within the fp32 tolerance."""
+    g = torch.Generator().manual_seed(tokens + experts)
+    logits = torch.randn(tokens, experts, generator=g).cuda()
+    capacity = max(4, 2 * tokens // experts)
+    want = _top2_gating(logits, capacity)
+    torch._dynamo.reset()
+    got = torch.compile(_top2_gating)(logits, capacity)
+    assert graphs.max_rel_err(got[0].cpu(), want[0].cpu()) <= 1e-5
+    assert torch.equal(got[1].cpu(), want[1].cpu())
+    assert graphs.max_rel_err(got[2].cpu(), want[2].cpu()) <= 1e-5
