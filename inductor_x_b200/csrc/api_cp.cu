@@ -17,7 +17,7 @@ int forward_update_t(const void* prev_attn, const float* prev_max, const float* 
                      float* out_max, float* out_sum, int S, int B, int N, int D, int64_t prev_ns,
                      int64_t cur_ns, int64_t out_ns, const ixb_devinfo* dev, cudaStream_t s) {
   auto kern = ixb::cp_forward_update_kernel<T>;
-  const size_t smem = (size_t)2 * N * sizeof(float2);   // weights of two rows in flight
+  const size_t smem = (size_t)2 * ixb::kCpRows * N * sizeof(float2);   // weights of two tiles in flight
   if (smem > 48 * 1024) return IXB_ERR_SHAPE;
   const int vph = D / ixb::Elem<T>::kVec;
   int shift = -1;
@@ -25,7 +25,7 @@ int forward_update_t(const void* prev_attn, const float* prev_max, const float* 
     for (shift = 0; (1 << shift) < vph; ++shift) {}
   int n = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
-  long long grid = (long long)S * B;
+  long long grid = (long long)B * ((S + ixb::kCpRows - 1) / ixb::kCpRows);
   const long long cap = (long long)dev->sm_count * n;
   if (grid > cap) grid = cap;
   kern<<<(unsigned)grid, 256, smem, s>>>((const T*)prev_attn, prev_max, prev_sum, (const T*)cur_attn, cur_max,

@@ -3,6 +3,7 @@
 // the pre-instantiated functors.  Header-only so that generated functor modules can
 // include the same code as the prebuilt library.
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -199,6 +200,38 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with programmatic stream serialization allowed: a kernel that calls pdl_wait()
+// before its first global access may be scheduled while the previous kernel of the stream
+// drains.  IXB_PDL=0 in the environment turns the attribute off.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("IXB_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+template <class K, class... Args>
+inline cudaError_t launch_pdl(K kern, unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
 // Named barrier over `nthreads` threads (a multiple of 32); id 0 is __syncthreads().

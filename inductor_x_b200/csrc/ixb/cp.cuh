@@ -20,11 +20,14 @@ namespace ixb {
 //   out = prev * (ps / l) + cur * (cs / l)          (fp32 math, stored in T)
 // The statistics are updated entry by entry, the attention scale uses entry 0
 // (attn_cp_test.py:24-33).
-// A CTA walks (s, b) rows of the attention tensors.  Per row, one thread per head first
-// merges that head's statistics (all eight entries, written out) and leaves the two
-// attention weights in shared memory; then the whole CTA streams the row, 128 bits per
-// access, looking its weights up by head.  The weight buffers alternate between rows, so one
-// barrier per row is enough.
+// A CTA walks tiles of kCpRows consecutive s for one b.  Per tile, one thread per (head, s)
+// first merges that pair's statistics (all eight entries, written out; the kCpRows entries
+// of a head are adjacent in memory, so a head's statistics move as whole 128-byte lines)
+// and leaves the two attention weights in shared memory; then the whole CTA streams the
+// tile's rows, 128 bits per access, looking its weights up by head.  The weight buffers
+// alternate between tiles, so one barrier per tile is enough.
+constexpr int kCpRows = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
     cp_forward_update_kernel(const T* __restrict__ prev_attn, const float* __restrict__ prev_max,
@@ -34,17 +37,21 @@ __global__ void __launch_bounds__(256)
                              float* __restrict__ out_sum, int S, int B, int N, int D,
                              long long prev_nstride, long long cur_nstride, long long out_nstride,
                              int head_shift) {
-  extern __shared__ float2 cp_weights[];   // [2][N]
+  extern __shared__ float2 cp_weights[];   // [2][kCpRows][N]
   constexpr int kVec = Elem<T>::kVec;
   const int H = N * D;
   const int vec_per_row = H / kVec;
   const int vph = D / kVec;              // vectors of one head; head_shift = log2(vph) or -1
-  const long long rows = (long long)S * B;
+  const long long tiles = (long long)B * ((S + kCpRows - 1) / kCpRows);
   int parity = 0;
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
-    const int s = (int)(row / B), b = (int)(row - (long long)s * B);
-    float2* w = cp_weights + parity * N;
-    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, parity ^= 1) {
+    const int b = (int)(tile % B);
+    const int s0 = (int)(tile / B) * kCpRows;
+    float2* w = cp_weights + parity * kCpRows * N;
+    for (int idx = threadIdx.x; idx < N * kCpRows; idx += blockDim.x) {
+      const int n = idx / kCpRows, sl = idx - n * kCpRows;
+      const int s = s0 + sl;
+      if (s >= S) continue;
       const long long bn = (long long)b * N + n;
       const long long po = bn * prev_nstride + (long long)s * 8;
       const long long co = bn * cur_nstride + (long long)s * 8;
@@ -67,23 +74,30 @@ __global__ void __launch_bounds__(256)
         l4.w = ps4.w * expf(pm4.w - m4.w) + cs4.w * expf(cm4.w - m4.w);
         *reinterpret_cast<float4*>(out_max + oo + q * 4) = m4;
         *reinterpret_cast<float4*>(out_sum + oo + q * 4) = l4;
-        if (q == 0) w[n] = make_float2(psx / l4.x, csx / l4.x);   // entry 0 scales the output
+        if (q == 0) w[sl * N + n] = make_float2(psx / l4.x, csx / l4.x);   // entry 0 scales the output
       }
     }
     __syncthreads();
-    const T* pa = prev_attn + row * H;
-    const T* ca = cur_attn + row * H;
-    T* oa = out_attn + row * H;
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-      const uint4 praw = ldg_stream(pa + (long long)v * kVec);
-      const uint4 craw = ldg_stream(ca + (long long)v * kVec);
-      const float2 ww = w[head_shift >= 0 ? (v >> head_shift) : (v / vph)];
-      float a[kVec], c[kVec];
-      unpack<T>(praw, a);
-      unpack<T>(craw, c);
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) a[i] = a[i] * ww.x + c[i] * ww.y;
-      stg_stream(oa + (long long)v * kVec, pack<T>(a));
+    for (int sl = 0; sl < kCpRows; ++sl) {
+      const int s = s0 + sl;
+      if (s >= S) break;
+      const long long row = (long long)s * B + b;
+      const T* pa = prev_attn + row * H;
+      const T* ca = cur_attn + row * H;
+      T* oa = out_attn + row * H;
+      const float2* wr = w + sl * N;
+      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+        const uint4 praw = ldg_stream(pa + (long long)v * kVec);
+        const uint4 craw = ldg_stream(ca + (long long)v * kVec);
+        const float2 ww = wr[head_shift >= 0 ? (v >> head_shift) : (v / vph)];
+        float a[kVec], c[kVec];
+        unpack<T>(praw, a);
+        unpack<T>(craw, c);
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) a[i] = a[i] * ww.x + c[i] * ww.y;
+        stg_stream(oa + (long long)v * kVec, pack<T>(a));
+      }
     }
   }
 }

@@ -209,6 +209,13 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   c.phase = 0;
   c.red = exchange + c.team * 2 * (TEAM / 32) * 4;
 
+  // Programmatic dependent launch: the next launch of the stream may place its CTAs as ours
+  // retire (its launch latency then overlaps our tail), and we touch no global memory
+  // until the launch before us has completed and flushed.  Both are no-ops for a launch
+  // without the attribute.
+  pdl_launch_dependents();
+  pdl_wait();
+
   typename Body::template Impl<VPT> body;
   body.init(p, c, body_smem);
 
@@ -387,8 +394,7 @@ cudaError_t launch_row(const typename Body::Params& p, long long rows, int cols,
   if (grid_override > 0) grid = grid_override;
   if (grid > groups) grid = groups;
   if (grid < 1) return cudaSuccess;
-  kern<<<(unsigned)grid, TEAM * TEAMS, smem, stream>>>(p, rows, cols);
-  return cudaGetLastError();
+  return launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, smem, stream, p, rows, cols);
 }
 
 }  // namespace ixb
