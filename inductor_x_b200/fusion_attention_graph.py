@@ -144,8 +144,62 @@ def b200_fa_meta(query, key, value, head_num, input_layout, pse=None, padding_ma
             torch.empty([1], dtype=torch.int64, device="meta"))
 
 
-def b200_fa_backward_impl(*args, **kwargs):
-    raise NotImplementedError("b200_fa_backward: the attention backward kernel is not built yet")
+def b200_fa_backward_impl(query, key, value, dy, head_num, input_layout, *, pse=None, padding_mask=None,
+                          atten_mask=None, softmax_max=None, softmax_sum=None, softmax_in=None,
+                          attention_in=None, scale_value=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX,
+                          next_tockens=TOKEN_MAX, inner_precise=0, seed=None, offset=None, numels=None,
+                          prefix=None, actual_seq_qlen=None, actual_seq_kvlen=None, sparse_mode=0,
+                          gen_mask_parallel=True, sync=False):
+    """Gradients of the fused attention from the saved log-sum-exp, recomputing the
+    probabilities block of heads by block of heads:
+
+        P = exp(Q K^T * m - lse);  dV = P^T dO;  dP = dO V^T
+        dS = P * (dP - rowsum(P * dP)) * m;  dQ = dS K;  dK = dS^T Q
+
+    This is NOT a hand-written kernel: the five products are library GEMMs (fp32) and the
+    element-wise steps are torch ops on the device.  It makes the op pair and the autograd
+    wrapper of the reference's surface (``npu_fusion_attention_graph.py:38-42,114-123``)
+    work end to end; a tcgen05 backward kernel is what would replace it."""
+    if pse is not None or padding_mask is not None or keep_prob != 1.0:
+        raise NotImplementedError("b200_fa_backward: pse, padding_mask and dropout are not supported")
+    if softmax_max is None or softmax_sum is None or attention_in is None:
+        raise ValueError("b200_fa_backward needs softmax_max, softmax_sum and attention_in from the forward")
+    causal = sparse_mode in CAUSAL_SPARSE_MODES
+    if atten_mask is not None and not causal:
+        raise NotImplementedError("b200_fa_backward: only causal masks (sparse_mode 2 or 3) are supported")
+    q = _to_bnsd(query, input_layout, head_num)
+    k = _to_bnsd(key, input_layout, head_num)
+    v = _to_bnsd(value, input_layout, head_num)
+    do = _to_bnsd(dy.contiguous(), input_layout, head_num)
+    B, N, Sq, D = q.shape
+    Sk = k.shape[2]
+    mult = 1.0 / scale_value
+    lse = softmax_max[..., 0] + torch.log(softmax_sum[..., 0])           # [B, N, Sq]
+    dq = torch.empty((B, N, Sq, D), dtype=torch.float32, device=q.device)
+    dk = torch.empty((B, N, Sk, D), dtype=torch.float32, device=q.device)
+    dv = torch.empty((B, N, Sk, D), dtype=torch.float32, device=q.device)
+    keep = None
+    if causal:
+        i = torch.arange(Sq, device=q.device).unsqueeze(1)
+        j = torch.arange(Sk, device=q.device).unsqueeze(0)
+        keep = j <= i + (Sk - Sq)
+    # heads per block: keep the fp32 score block under about 256 MiB
+    per = max(1, min(N, (64 << 20) // max(1, Sq * Sk)))
+    for b in range(B):
+        for n0 in range(0, N, per):
+            sl = (b, slice(n0, n0 + per))
+            qf, kf, vf, dof = q[sl].float(), k[sl].float(), v[sl].float(), do[sl].float()
+            p = torch.matmul(qf, kf.transpose(-1, -2)).mul_(mult).sub_(lse[sl].unsqueeze(-1)).exp_()
+            if keep is not None:
+                p = p * keep
+            dv[sl] = torch.matmul(p.transpose(-1, -2), dof)
+            dp = torch.matmul(dof, vf.transpose(-1, -2))
+            # rowsum(P * dP) is rowsum(dO * O) with the exact O, not the 16-bit one that was stored
+            ds = dp.sub_((p * dp).sum(-1, keepdim=True)).mul_(p).mul_(mult)
+            dq[sl] = torch.matmul(ds, kf)
+            dk[sl] = torch.matmul(ds.transpose(-1, -2), qf)
+    cast = lambda t, like: _from_bnsd(t.to(like.dtype), input_layout)
+    return cast(dq, query), cast(dk, key), cast(dv, value), None
 
 
 def b200_fa_backward_meta(query, key, value, dy, head_num, input_layout, **kwargs):
@@ -174,8 +228,8 @@ b200_meta.impl("b200_sdpa", b200_sdpa_meta)
 
 
 class B200GraphAttentionFunction(Function):
-    """Autograd wrapper (``NpuGraphAttentionFunction``, ``:88-123``).  Forward only for now:
-    backward raises until the backward kernel exists."""
+    """Autograd wrapper (``NpuGraphAttentionFunction``, ``:88-123``): forward on the tcgen05
+    kernel, backward through ``b200_fa_backward`` (library GEMMs, see there)."""
 
     @staticmethod
     def forward(ctx, query, key, value, head_num, input_layout, pse=None, padding_mask=None,

@@ -117,3 +117,41 @@ def test_attention_argument_errors(cuda):
         ops.fused_attention(q, k, k, 1.0, causal=True)  # causal with Sk < Sq
     empty = ops.fused_attention(q[:, :, :0], k, k, 1.0)
     assert empty.shape == (1, 1, 0, 128)
+
+
+@pytest.mark.parametrize("layout", ["BNSD", "BSND", "BSH"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_autograd_through_the_attention_op(layout, causal):
+    """Gradients through `b200_fusion_attention_graph` (forward on the tcgen05 kernel,
+    backward through `b200_fa_backward`) against autograd through eager fp32 attention on
+    the same inputs.  Tolerance 2e-2 relative to max(|expected|, rms) per tensor: the
+    forward output and the saved log-sum-exp come from 16-bit operands."""
+    from inductor_x_b200.fusion_attention_graph import b200_fusion_attention_graph
+
+    B, N, S, D = 2, 3, 192, 128
+    g = torch.Generator().manual_seed(17)
+    q, k, v, dy = (torch.randn(B, N, S, D, generator=g).to(torch.bfloat16).cuda() for _ in range(4))
+    scale = 1.0 / math.sqrt(D)
+
+    def to_layout(t):
+        if layout == "BNSD":
+            return t.clone()
+        if layout == "BSND":
+            return t.transpose(1, 2).contiguous()
+        return t.transpose(1, 2).reshape(B, S, N * D).contiguous()
+
+    ql, kl, vl = (to_layout(t).requires_grad_(True) for t in (q, k, v))
+    out = b200_fusion_attention_graph(ql, kl, vl, N, layout, scale=1.0 / scale,
+                                      sparse_mode=3 if causal else 0)[0]
+    out.backward(to_layout(dy))
+
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+    s = torch.matmul(qr, kr.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=s.device).tril(), float("-inf"))
+    ref = torch.matmul(torch.softmax(s, -1), vr)
+    ref.backward(dy.float())
+    assert graphs.max_rel_err(out.detach().float().cpu(), to_layout(ref.detach()).cpu()) <= 2e-2
+    for got, want in ((ql.grad, qr.grad), (kl.grad, kr.grad), (vl.grad, vr.grad)):
+        assert got is not None and got.dtype == torch.bfloat16
+        assert graphs.max_rel_err(got.float().cpu(), to_layout(want).cpu()) <= 2e-2
