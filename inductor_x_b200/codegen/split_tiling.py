@@ -54,7 +54,7 @@ def narrowest_dtype(dtypes: Iterable[torch.dtype]) -> torch.dtype:
 
 MAX_TEAM = 1024
 MIN_TEAM = 8          # teams narrower than a warp serve rows of a few vectors
-MAX_VPT = 8
+MAX_VPT = 32         # beyond 8 the row no longer fits the register file and spills: slow but correct
 
 
 def choose_row_config(rnumel: int, dtype: torch.dtype, rows: Optional[int] = None,

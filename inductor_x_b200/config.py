@@ -37,7 +37,7 @@ l2_bytes = 126 * 1024 * 1024
 #: bytes of one coalesced per-thread access (the reference's npu_block is 32)
 vector_bytes = 16
 #: longest reduced row, in 128-bit vectors, that the persistent row template holds on chip
-max_row_vectors = 1024 * 8
+max_row_vectors = 1024 * 32
 
 BYTES_PER_ELEMENT = {
     torch.float32: 4, torch.float16: 2, torch.bfloat16: 2, torch.float64: 8, torch.int64: 8,

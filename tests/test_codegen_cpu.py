@@ -124,6 +124,8 @@ def test_launch_chooser():
     assert (c.team, c.vpt, c.teams) == (8, 1, 16)
     c = st.choose_row_config(32768, torch.float32)                   # beyond 1024 x 2 vectors
     assert (c.team, c.vpt) == (1024, 8)
+    c = st.choose_row_config(128256, torch.float32)                  # a vocabulary-sized fp32 row: spills, but runs
+    assert (c.team, c.vpt) == (1024, 32)
     assert st.choose_row_config(1 << 20, torch.float32) is None
     assert st.choose_pointwise_vec([torch.float32, torch.bfloat16]) == 8
     assert st.choose_pointwise_vec([torch.float32]) == 4

@@ -293,3 +293,15 @@ def test_moe_top2_gating_graph(tokens, experts):
     assert graphs.max_rel_err(got[0].cpu(), want[0].cpu()) <= 1e-5
     assert torch.equal(got[1].cpu(), want[1].cpu())
     assert graphs.max_rel_err(got[2].cpu(), want[2].cpu()) <= 1e-5
+
+
+def test_vocabulary_sized_row():
+    """log_softmax over a 128,256-wide fp32 row (a Llama-3 vocabulary): longer than the
+    register file holds, so the generated kernel spills, but it must still be one correct
+    kernel rather than an error."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(24, 128256, generator=g) * 3).cuda()
+    torch._dynamo.reset()
+    got = torch.compile(lambda t: torch.log_softmax(t, -1))(x)
+    want = torch.log_softmax(x.double(), -1)
+    assert graphs.max_rel_err(got.cpu().double(), want.cpu()) <= 1e-5
