@@ -127,6 +127,13 @@ class SoftmaxLayerNorm:
         ops.softmax_layernorm(self.xs[k], *self.params, 1e-5, out=self.ys[k])
         return 1  # kernels launched
 
+    def graph(self):
+        import torch.nn.functional as F
+
+        cols = self.cols
+        fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (cols,), ga, be, 1e-5)
+        return fn, lambda i: (self.xs[i % len(self.xs)], *self.params)
+
     def e2e_setup(self, device):
         from inductor_x_b200.host_io import HostRowPipeline
 
@@ -183,6 +190,11 @@ class AffineGeluRowSum:
         ops.affine_gelu_rowsum(self.xs[i % len(self.xs)], self.w, self.b, out=self.out)
         return 1
 
+    def graph(self):
+        import torch.nn.functional as F
+
+        return (lambda x, w, b: F.gelu(x * w + b).sum(-1)), lambda i: (self.xs[i % len(self.xs)], self.w, self.b)
+
     def e2e_setup(self, device):
         self.h_x = self.host["x"].pin_memory()
         self.h_o = torch.empty(self.rows).pin_memory()
@@ -234,6 +246,9 @@ class PermutedAmax:
         self.out = ops.outer_reduce(self.xs[i % len(self.xs)].view(a * b, c, d), "amax", rsplit=1)
         return 1
 
+    def graph(self):
+        return (lambda t: t.permute(0, 2, 1, 3).amax(1)), lambda i: (self.xs[i % len(self.xs)],)
+
     def e2e_setup(self, device):
         self.h_x = self.host.pin_memory()
         self.d_x = torch.empty_like(self.xs[0])
@@ -271,6 +286,9 @@ class PermutedSum(PermutedAmax):
         a, b, c, d = self.shape
         self.out = ops.short_row_reduce(self.xs[i % len(self.xs)], "sum", (c * b, 1, b))
         return 1
+
+    def graph(self):
+        return (lambda t: t.permute(0, 2, 1, 3).sum(3)), lambda i: (self.xs[i % len(self.xs)],)
 
     def e2e_setup(self, device):
         self.h_x = self.host.pin_memory()
@@ -323,6 +341,9 @@ class IndexSelect:
 
         self.out = ops.index_select_rows(self.table, self.idxs[i % len(self.idxs)], check_bounds=False)
         return 1
+
+    def graph(self):
+        return (lambda t, i: t.index_select(0, i)), lambda i: (self.table, self.idxs[i % len(self.idxs)])
 
     def e2e_setup(self, device):
         self.h_idx = self.host["idx"].pin_memory()
@@ -586,6 +607,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the Python enqueue loop instead of a CUDA graph")
+    ap.add_argument("--compiled", action="store_true",
+                    help="run the workload's graph through torch.compile (generated kernels) instead of "
+                         "the prebuilt entry point of the kernel library")
     ap.add_argument("--c4-batch", type=int, default=0,
                     help="override the attention batch (profiling captures on a smaller case)")
     args = ap.parse_args()
@@ -625,6 +649,24 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.compiled:
+        # the same graph through torch.compile: Inductor with this package's backend, every
+        # fused group a generated kernel (counted through the module loader's launch counters)
+        if not hasattr(wl, "graph"):
+            raise SystemExit(f"--compiled: workload {args.workload} has no graph form (c5 is always compiled)")
+        import inductor_x_b200  # noqa: F401  (registers the backend)
+        from inductor_x_b200.codegen import jit
+
+        fn, graph_args = wl.graph()
+        compiled = torch.compile(fn)
+
+        def compiled_step(i):
+            before = sum(k.launches for k in jit._loaded.values())
+            wl.out = compiled(*graph_args(i))
+            return sum(k.launches for k in jit._loaded.values()) - before
+
+        wl.step = compiled_step
 
     for i in range(max(args.warmup, 3)):
         wl.step(i)
@@ -732,7 +774,7 @@ def main():
         unit = "TFLOP/s" if tensor_bound else "GB/s"
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tpath):
+        if os.path.exists(tpath) and not args.compiled:   # the captures are of the prebuilt kernels
             with open(tpath) as f:
                 traffic = json.load(f).get(wl.name)
         line = {
@@ -745,6 +787,8 @@ def main():
                        "l2": "working set per step exceeds the 126 MB L2 and steps rotate over "
                              f"{len(getattr(wl, 'xs', getattr(wl, 'idxs', [0])))} distinct buffer sets",
                        "sharding": f"rows split over {world} GPU(s), no collective",
+                       "path": ("torch.compile -> generated kernels" if args.compiled
+                                else "prebuilt kernel library entry point"),
                        "timed_region": "one CUDA graph of the K launches" if graph is not None else "enqueue loop"},
             "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                          "unit": unit, "frac": achieved / peak, "traffic": traffic,
