@@ -310,4 +310,22 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 }
 #endif
 
+// gelu_erf_fast on two values: same operations, the polynomial on packed pairs.
+__device__ __forceinline__ float2 gelu_erf_fast2(float2 v) {
+  const float2 a = make_float2(fabsf(v.x), fabsf(v.y));
+  const float2 t = make_float2(fminf(a.x, 12.f), fminf(a.y, 12.f));
+  // coefficients negated: the polynomial yields -g, the argument of the exponential
+  float2 g = fma2(make_float2(3.309498788439669e-05f, 3.309498788439669e-05f), t,
+                  make_float2(-0.0007692387443967164f, -0.0007692387443967164f));
+  g = fma2(g, t, make_float2(0.008080779574811459f, 0.008080779574811459f));
+  g = fma2(g, t, make_float2(-0.05341219902038574f, -0.05341219902038574f));
+  g = fma2(g, t, make_float2(-0.45877090096473694f, -0.45877090096473694f));
+  g = fma2(g, t, make_float2(-1.1512017250061035f, -1.1512017250061035f));
+  g = fma2(g, t, make_float2(-0.999993085861206f, -0.999993085861206f));
+  float ex, ey;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(g.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ey) : "f"(g.y));
+  return make_float2(fmaf(-a.x, ex, fmaxf(v.x, 0.f)), fmaf(-a.y, ey, fmaxf(v.y, 0.f)));
+}
+
 }  // namespace ixb

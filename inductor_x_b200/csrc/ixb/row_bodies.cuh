@@ -44,6 +44,7 @@ struct AffineGeluRowSum {
     __device__ __forceinline__ void row(const Params& p, Ctx& c, long long r,
                                         const uint4 (&raw)[1][VPT]) {
       float acc = 0.f;
+      float2 acc2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float x[4], w[4], b[4];
@@ -58,10 +59,24 @@ struct AffineGeluRowSum {
           unpack<float>(c.template load<false>(p.w, i), w);
           unpack<float>(c.template load<false>(p.b, i), b);
         }
+        if constexpr (Ctx::kAligned) {
+          // whole vectors are valid or not: two elements per issue slot through the affine
+          // step and the polynomial of the GELU
+          if (c.valid(i)) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (c.ok(i, j)) acc += gelu_erf_fast(fmaf(x[j], w[j], b[j]));
+            for (int j = 0; j < 4; j += 2) {
+              const float2 v = fma2(make_float2(x[j], x[j + 1]), make_float2(w[j], w[j + 1]),
+                                    make_float2(b[j], b[j + 1]));
+              acc2 = add2(acc2, gelu_erf_fast2(v));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c.ok(i, j)) acc += gelu_erf_fast(fmaf(x[j], w[j], b[j]));
+        }
       }
+      acc += acc2.x + acc2.y;
       acc = c.template reduce<SumOp>(acc);
       if (c.lane == 0) p.out[r] = acc;
     }
