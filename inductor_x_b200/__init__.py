@@ -72,20 +72,32 @@ def _register_device_interface():
     register_interface_for_device("cuda", B200Interface)
 
 
+def _enable_online_softmax_pattern():
+    """Inductor rewrites softmax's max and sum into one ``online_softmax_reduce`` only when its
+    own Triton backend is selected for the device; the row template has that reduction too
+    (one exchange per row instead of two), so the check is widened to this backend."""
+    import torch._inductor.fx_passes.post_grad as post_grad
+    from torch._inductor import config as inductor_config
+
+    def extra_check(match):
+        device_type = match.kwargs["x"].meta["val"].device.type
+        return inductor_config.online_softmax and (device_type == "cuda" or config.dry_run)
+
+    post_grad.prepare_softmax_extra_check = extra_check
+
+
 def register():
     """Perform the registrations (idempotent).  Called at import unless IXB_REGISTER=0."""
     global _registered
     if _registered:
         return
-    from torch._inductor import lowering as inductor_lowering
-
     from .decomposition import _register_b200_inductor_decompositions
-    from .lowering import _register_b200_inductor_fallbacks, make_reduction
+    from .lowering import _register_b200_inductor_fallbacks
 
     _inductor_register_backend_for_device()
     _inductor_register_device_op_overrides()
     _register_device_interface()
-    inductor_lowering.make_reduction = make_reduction
+    _enable_online_softmax_pattern()
     _register_b200_inductor_fallbacks()
     _register_b200_inductor_decompositions()
     from . import fusion_attention_graph

@@ -142,34 +142,113 @@ def is_vector_contiguous(expr: sympy.Expr, root: sympy.Symbol, vec: int, numel: 
     return True
 
 
+def _axis_pieces(expr: sympy.Expr, root: sympy.Symbol):
+    """Split ``expr`` into (rest, pieces): ``pieces`` lists ``(coeff, divisor, modulus)`` for
+    every term that is an integer multiple of ``root``, ``FloorDiv(root, d)`` or
+    ``ModularIndexing(root, d, m)`` (modulus None when absent); ``rest`` is the sum of the
+    terms free of ``root``.  None when ``root`` occurs in any other shape."""
+    from torch.utils._sympy.functions import FloorDiv, ModularIndexing
+
+    rest = sympy.S.Zero
+    pieces = []
+    for term in sympy.Add.make_args(sympy.expand(expr)):
+        if root not in term.free_symbols:
+            rest += term
+            continue
+        coeff, atom = term.as_coeff_Mul()
+        if not coeff.is_Integer:
+            return None
+        if atom == root:
+            pieces.append((int(coeff), 1, None))
+        elif isinstance(atom, ModularIndexing) and atom.args[0] == root and all(a.is_Integer for a in atom.args[1:]):
+            pieces.append((int(coeff), int(atom.args[1]), int(atom.args[2])))
+        elif isinstance(atom, FloorDiv) and atom.args[0] == root and atom.args[1].is_Integer:
+            pieces.append((int(coeff), int(atom.args[1]), None))
+        else:
+            return None
+    return rest, pieces
+
+
 def reduction_stride(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol, xnumel: int,
                      rnumel: int) -> Optional[int]:
     """Stride of the flat reduction variable in ``expr`` if it is one constant over the
     whole range (``expr(x, r) == expr(x, 0) + stride * r``), else None.  Stride 1 means the
     access walks the row contiguously (row template); a larger constant stride means an
     outer reduction; None means the reduced range is itself a flattening of several axes
-    with different strides."""
+    with different strides, or has a shape this analysis does not understand.
+
+    Decided from the structure of the expression: the terms in ``r`` must be digits of a
+    mixed-radix split of ``r`` - ``ModularIndexing(r, d_i, m_i)`` with ``d_0 == 1`` and
+    ``d_{i+1} == d_i * m_i``, the last one reaching the end of the range - and digit ``i``
+    must carry the coefficient ``stride * d_i``.  Then the sum is ``stride * r`` exactly."""
     if expr.free_symbols - {x_root, r_root}:
         return None
     if r_root not in expr.free_symbols:
         return 0
-    xs = sorted({0, 1, xnumel - 1, xnumel // 2, xnumel // 3} & set(range(xnumel)))
-    rs = sorted({1, 2, 3, rnumel - 1, rnumel // 2, rnumel // 3 + 1} & set(range(1, rnumel)))
-    stride = None
-    for x in xs:
-        base = _eval(expr, {x_root: x, r_root: 0})
-        if base is None:
+    if rnumel == 1:
+        return 1
+    split = _axis_pieces(expr, r_root)
+    if split is None:
+        return None
+    _, pieces = split
+    merged: Dict[tuple, int] = {}
+    for coeff, d, m in pieces:
+        if m is not None and d * m >= rnumel:
+            m = None                       # the modulus never wraps inside the range
+        merged[(d, m)] = merged.get((d, m), 0) + coeff
+    digits = sorted(merged.items(), key=lambda kv: kv[0][0])
+    if not digits or digits[0][0][0] != 1:
+        return None
+    stride = digits[0][1]
+    reach = 1
+    for (d, m), coeff in digits:
+        if d != reach or coeff != stride * d:
             return None
-        for r in rs:
-            v = _eval(expr, {x_root: x, r_root: r})
-            if v is None or (v - base) % r != 0:
-                return None
-            s = (v - base) // r
-            if stride is None:
-                stride = s
-            elif s != stride:
-                return None
-    return stride if stride is not None else (1 if rnumel == 1 else None)
+        if m is None:
+            reach = None
+            break
+        reach = d * m
+    if reach is not None and reach < rnumel:
+        return None
+    if digits[-1][0][1] is not None and reach is not None:
+        return None
+    # nothing may follow the digit that reaches the end of the range
+    last_open = [i for i, ((d, m), _) in enumerate(digits) if m is None]
+    if last_open and last_open[0] != len(digits) - 1:
+        return None
+    return stride
+
+
+def row_starts_aligned(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol, vec: int) -> bool:
+    """True when the element offset of every row start (``r == 0``) is a multiple of
+    ``vec``: every term in the kept index carries a coefficient that is a multiple of
+    ``vec``, and so does the constant.  With a 16-byte aligned base pointer each row then
+    starts on a 16-byte boundary."""
+    if expr.free_symbols - {x_root, r_root}:
+        return False
+    at0 = expr.subs({r_root: 0}) if r_root in expr.free_symbols else expr
+    split = _axis_pieces(at0, x_root)
+    if split is None:
+        return False
+    rest, pieces = split
+    if rest.free_symbols or not rest.is_Integer or int(rest) % vec != 0:
+        return False
+    return all(coeff % vec == 0 for coeff, _, _ in pieces)
+
+
+def x_contiguous_for_all_r(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol, vec: int) -> bool:
+    """Vector contiguity along the kept index for every value of the reduced index: the
+    terms in ``x`` must be vector-contiguous by structure (``vector_access``) and no term
+    may mix the two indices."""
+    if expr.free_symbols - {x_root, r_root}:
+        return False
+    split = _axis_pieces(expr, r_root)
+    if split is None:
+        return False
+    rest, _ = split
+    if r_root in rest.free_symbols or x_root not in rest.free_symbols:
+        return False
+    return vector_access(rest, x_root, vec)[0]
 
 
 def x_stride_at_row_start(expr: sympy.Expr, x_root: sympy.Symbol, r_root: sympy.Symbol,

@@ -12,9 +12,11 @@ from __future__ import annotations
 
 import ctypes
 import hashlib
+import json
 import os
 import re
 import subprocess
+import sys
 import threading
 import time
 
@@ -32,16 +34,27 @@ _loaded: dict = {}
 class GeneratedKernel:
     """Callable handle of one compiled functor module."""
 
-    def __init__(self, key: str, path: str, meta: dict):
+    def __init__(self, key: str, path: str, meta: dict, src: str = ""):
         self.key = key
         self.path = path
         self.meta = dict(meta)
+        self.src = src
+        self.launches = 0
+        self.shape = None            # launch shape in use, once a measurement picked one
+        self.tuning = None           # [(shape, us)] of the last measurement
+        self._bind(path)
+        tune = self.meta.get("tune")
+        self._tune_pending = bool(
+            tune and tune.get("candidates") and tune.get("idempotent") and config.autotune
+            and tune.get("rows", 0) * tune.get("row_bytes", 0) >= config.autotune_min_bytes)
+
+    def _bind(self, path: str) -> None:
         self.lib = ctypes.CDLL(path)
         self.fn = self.lib.ixb_gen_launch
         self.fn.restype = ctypes.c_int
         self.fn.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_longlong),
                             ctypes.c_void_p]
-        self.launches = 0
+        self.path = path
 
     def run(self, *args, stream=None):
         ptrs, ints = [], []
@@ -56,6 +69,9 @@ class GeneratedKernel:
             stream = torch.cuda.current_stream().cuda_stream
         pa = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
         ia = (ctypes.c_longlong * max(len(ints), 1))(*ints)
+        if self._tune_pending and not torch.cuda.is_current_stream_capturing():
+            self._tune_pending = False
+            self._autotune(pa, ia, stream)
         if config.profile_bandwidth:
             return self._run_profiled(pa, ia, stream, args)
         rc = self.fn(pa, ia, stream)
@@ -63,6 +79,81 @@ class GeneratedKernel:
         if rc != 0:
             raise RuntimeError(f"generated kernel {self.meta.get('name', self.key)} failed to launch: "
                                f"cudaError {rc}")
+        if self.meta.get("bounds"):
+            self._raise_on_bad_index()
+
+    def _raise_on_bad_index(self) -> None:
+        """Debug builds: read the module's status words (this synchronises) and report an
+        out-of-range data-dependent index as eager mode would."""
+        status = (ctypes.c_ulonglong * 2)()
+        rc = self.lib.ixb_gen_bounds(status)
+        if rc != 0:
+            raise RuntimeError(f"reading the bounds status failed: cudaError {rc}")
+        if status[0]:
+            bad = ctypes.c_longlong(status[1]).value
+            raise IndexError(f"generated kernel {self.meta.get('name', self.key)}: {status[0]} index value(s) "
+                             f"out of range, e.g. {bad}")
+
+    # ---- measured choice of the launch shape ----------------------------------------------
+    # Stands where the reference's autotuner benchmarks its tile configurations and caches the
+    # best one (inductor_x/npu_triton_heuristics.py:53-266, 302-435).  The candidates are the
+    # same body built with other launch-shape macros; each is timed with CUDA events on the
+    # caller's own tensors (the kernel writes only its outputs, so repeating it is harmless)
+    # and the fastest is kept, in memory and in a small JSON file beside the modules.
+    def _autotune(self, pa, ia, stream) -> None:
+        tune = self.meta["tune"]
+        default = tuple(tune["default"])
+        decision = _read_decision(self.key)
+        if decision is not None:
+            shape = tuple(decision["shape"])
+            if shape != default:
+                try:
+                    self._bind(compile_source(self.src, shape=shape))
+                except RuntimeError:
+                    return
+            self.shape, self.tuning = shape, [tuple(t) for t in decision.get("timings", [])]
+            return
+        shapes = [default] + [tuple(c) for c in tune["candidates"]][: config.autotune_max_candidates]
+        built = compile_variants(self.src, shapes[1:])
+        libs = [(default, self.path)] + [(sh, so) for sh, so in built if so is not None]
+        results = []
+        n = config.autotune_launches
+        for shape, so in libs:
+            lib = ctypes.CDLL(so)
+            fn = lib.ixb_gen_launch
+            fn.restype = ctypes.c_int
+            fn.argtypes = self.fn.argtypes
+            ok = True
+            for _ in range(2):
+                ok = ok and fn(pa, ia, stream) == 0
+            if not ok:
+                continue
+            # host clock around a device-wide synchronise on both sides: independent of which
+            # stream the caller launches on; n back-to-back launches amortise the enqueue cost
+            best = float("inf")
+            for _ in range(3):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(n):
+                    ok = ok and fn(pa, ia, stream) == 0
+                torch.cuda.synchronize()
+                best = min(best, (time.perf_counter() - t0) * 1e6 / n)
+            if ok:
+                results.append((shape, best, so))
+        if not results:
+            return
+        results.sort(key=lambda r: r[1])
+        shape, us, so = results[0]
+        self.shape = shape
+        self.tuning = [(sh, round(t, 2)) for sh, t, _ in results]
+        if so != self.path:
+            self._bind(so)
+        nbytes = 2.0 * tune["rows"] * tune["row_bytes"]
+        _write_decision(self.key, dict(shape=list(shape), us=us, gbs=nbytes / us / 1e3,
+                                       timings=[[list(sh), t] for sh, t in self.tuning]))
+        if config.autotune_verbose:
+            print(f"[ixb autotune] {self.key}: " + ", ".join(f"{sh}={t:.1f}us" for sh, t in self.tuning),
+                  file=sys.stderr, flush=True)
 
     def _run_profiled(self, pa, ia, stream, args):
         """ms / GB / GB/s per launch, from the bytes of the tensor arguments
@@ -77,6 +168,28 @@ class GeneratedKernel:
         ms = e0.elapsed_time(e1)
         gb = sum(a.numel() * a.element_size() for a in args if isinstance(a, torch.Tensor)) / 1e9
         print(f"{self.meta.get('name', self.key)}: {ms:.3f}ms    {gb:.3f}GB    {gb / (ms / 1e3):.2f}GB/s")
+
+
+def _decision_path(key: str) -> str:
+    return os.path.join(config.cache_dir, f"tune_{key}.json")
+
+
+def _read_decision(key: str):
+    try:
+        with open(_decision_path(key)) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return None
+
+
+def _write_decision(key: str, decision: dict) -> None:
+    try:
+        tmp = f"{_decision_path(key)}.{os.getpid()}.tmp"
+        with open(tmp, "w") as f:
+            json.dump(decision, f)
+        os.replace(tmp, _decision_path(key))
+    except OSError:
+        pass
 
 
 _headers_digest = None
@@ -101,32 +214,50 @@ def source_key(src: str) -> str:
     return hashlib.sha256(_template_digest() + src.encode()).hexdigest()[:24]
 
 
-def compile_source(src: str, verbose: bool = False) -> str:
-    """Compile ``src`` into the cache directory (if not already there); returns the .so path."""
+SHAPE_MACROS = ("IXB_ROW_TEAM", "IXB_ROW_TEAMS", "IXB_ROW_VPT", "IXB_GEN_MIN_CTAS", "IXB_ROW_PF")
+
+
+def compile_source(src: str, verbose: bool = False, shape=None) -> str:
+    """Compile ``src`` into the cache directory (if not already there); returns the .so path.
+    ``shape`` = (team, teams, vpt, min_ctas, prefetch) builds a row module in another launch
+    shape than the one its source names."""
     key = source_key(src)
     os.makedirs(config.cache_dir, exist_ok=True)
-    so = os.path.join(config.cache_dir, f"ixbgen_{key}.so")
+    suffix = "" if shape is None else "_" + "x".join(str(int(v)) for v in shape)
+    so = os.path.join(config.cache_dir, f"ixbgen_{key}{suffix}.so")
     if os.path.exists(so):
         return so
     cu = os.path.join(config.cache_dir, f"ixbgen_{key}.cu")
-    with open(cu, "w") as f:
-        f.write(src)
-    tmp = f"{so}.{os.getpid()}.tmp"
+    if not os.path.exists(cu):
+        tmp_cu = f"{cu}.{os.getpid()}.{threading.get_ident()}.tmp"
+        with open(tmp_cu, "w") as f:
+            f.write(src)
+        os.replace(tmp_cu, cu)
+    tmp = f"{so}.{os.getpid()}.{threading.get_ident()}.tmp"
     t0 = time.time()
     # A row module states how many CTAs per SM its registers are bounded for.  If ptxas had
     # to spill under that bound the module is rebuilt with a looser one.
+    defines = []
     m = re.search(r"#define IXB_GEN_MIN_CTAS (\d+)", src)
+    n = int(m.group(1)) if m else None
+    if shape is not None:
+        team, teams, vpt, n, pf = (int(v) for v in shape)
+        defines = [f"-DIXB_ROW_TEAM={team}", f"-DIXB_ROW_TEAMS={teams}", f"-DIXB_ROW_VPT={vpt}", f"-DIXB_ROW_PF={pf}"]
     bounds = [None]
-    if m:
-        n = int(m.group(1))
+    if n is not None:
         bounds = [n] + [b for b in (6, 4, 3, 2, 1) if b < n]
+    if shape is not None:
+        bounds = [n]          # a candidate is built exactly as named; one that spills is dropped
     for bound in bounds:
         extra = [] if bound is None else [f"-DIXB_GEN_MIN_CTAS={bound}"]
-        cmd = ["nvcc", *_NVCC_FLAGS, "-Xptxas", "-v", *extra, "-I", _CSRC, "-o", tmp, cu]
+        cmd = ["nvcc", *_NVCC_FLAGS, "-Xptxas", "-v", *defines, *extra, "-I", _CSRC, "-o", tmp, cu]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed for generated kernel {cu}:\n{proc.stderr[-4000:]}")
         spills = [int(x) for x in re.findall(r"(\d+) bytes spill stores", proc.stderr)]
+        if shape is not None and spills and max(spills) > config.autotune_spill_bytes:
+            os.remove(tmp)
+            raise RuntimeError(f"launch shape {shape} spills {max(spills)} bytes")
         if bound in (None, 1) or not any(spills):
             break
     os.replace(tmp, so)
@@ -135,12 +266,32 @@ def compile_source(src: str, verbose: bool = False) -> str:
     return so
 
 
+def compile_variants(src: str, shapes):
+    """Build ``src`` in each launch shape, in parallel; [(shape, path or None)]."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(shape):
+        try:
+            return shape, compile_source(src, shape=shape)
+        except RuntimeError:
+            return shape, None
+
+    if not shapes:
+        return []
+    with ThreadPoolExecutor(max_workers=min(len(shapes), config.compile_threads)) as pool:
+        return list(pool.map(one, shapes))
+
+
 def load_kernel(src: str, **meta) -> GeneratedKernel:
     """Entry point named in generated wrapper code."""
     key = source_key(src)
     with _lock:
         k = _loaded.get(key)
         if k is None:
-            k = GeneratedKernel(key, compile_source(src), meta)
+            k = GeneratedKernel(key, compile_source(src), meta, src)
             _loaded[key] = k
+            tune = meta.get("tune")
+            if config.dry_run and config.prebuild_candidates and tune and tune.get("candidates"):
+                # host-only build step: have every launch shape ready for the measurement
+                compile_variants(src, [tuple(c) for c in tune["candidates"]][: config.autotune_max_candidates])
     return k

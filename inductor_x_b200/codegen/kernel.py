@@ -36,6 +36,10 @@ from . import split_tiling
 from .overrides import (B200Overrides, CPP_TYPE, FLOAT_DTYPES, INT_DTYPES, IxbExprPrinter,
                         constant_literal)
 
+
+def config_bytes(dtype: torch.dtype) -> int:
+    return ixb_config.BYTES_PER_ELEMENT.get(dtype, 8)
+
 G = "ixb::gen::"
 
 REDUCTION_OPS = {
@@ -43,8 +47,25 @@ REDUCTION_OPS = {
 }
 
 
+INT_REDUCTION_OPS = {"sum": "ISum", "prod": "IProd", "max": "IMax", "min": "IMin"}
+
+#: registers a thread may spend on operands that are the same for every row
+MAX_CONST_REGS = 64
+#: streamed operands fetched one row ahead as raw 128-bit vectors
+MAX_STAGED = 2
+
+
 class UnsupportedByTemplates(NotImplementedError):
     """The fused group needs something no B200 template provides yet."""
+
+
+class B200CSEVariable(CSEVariable):
+    """Records the op and operands every value came from: the emitter's peephole rewrites
+    (fused multiply-add, folded scalar factors, reuse of the online-softmax exponentials,
+    sums carried by an earlier exchange) look operands up in that table."""
+
+    def update_on_args(self, name, args, kwargs):
+        V.kernel.note_op(self, name, args, kwargs)
 
 
 class B200Kernel(SIMDKernel):
@@ -61,6 +82,14 @@ class B200Kernel(SIMDKernel):
         self._ph: dict = {}
         self._ph_by_key: dict = {}
         self._row_prefetch: list = []
+        self.dag: dict = {}          # value name -> (op name, operands)
+        self.scalars: set = set()    # values that do not vary along the reduced row
+        self.consts: list = []       # hoisted row-invariant operands: (member, pointer text, element count)
+        self.staged: list = []       # operands fetched a row ahead: (member, ctype, pointer text)
+        self.const_of: dict = {}     # value name -> Consts member text
+        self.online: dict = {}       # name of a softmax input -> its online-softmax exchange
+        self.online_exp: dict = {}   # name of exp(input - max) -> exchange
+        self.checked_indices = 0     # data-dependent indices checked on the device (debug builds)
         self.x_indexing = IndentedBuffer()
         self.r_indexing = IndentedBuffer()
         super().__init__(tiling, **kwargs)
@@ -77,6 +106,65 @@ class B200Kernel(SIMDKernel):
             self._outer_vec = split_tiling.choose_pointwise_vec(self._node_dtypes())
         else:
             self.vec = split_tiling.choose_pointwise_vec(self._node_dtypes())
+
+    def create_cse_var(self, *args, **kwargs):
+        return B200CSEVariable(*args, **kwargs)
+
+    # ------------------------------------------------------------------ value table
+    def note_op(self, var, name, args, kwargs=None) -> None:
+        # a peephole that replaced the op by a different one says so (pending_dag)
+        entry = getattr(self, "pending_dag", None) or (name, args, kwargs or {})
+        self.pending_dag = None
+        self.dag.setdefault(var.name, entry)
+        if name == "exp" and getattr(self, "pending_online_exp", None) is not None:
+            self.online_exp[var.name] = self.pending_online_exp
+        self.pending_online_exp = None
+        if name in ("load", "reduction"):
+            return
+        if name == "index_expr":
+            if self.is_row and not self._has_reduction_var(self.prepare_indexing(args[0])):
+                self.scalars.add(var.name)
+            return
+        if not self.is_row:
+            return
+        if all(str(a) in self.scalars for a in args if isinstance(a, CSEVariable)):
+            self.scalars.add(var.name)
+
+    def resolve(self, v):
+        """The value ``v`` names, seen through casts between floating types (all floating
+        values are fp32 inside a kernel)."""
+        for _ in range(8):
+            d = self.dag.get(str(v))
+            if d is None or d[0] != "to_dtype":
+                break
+            src = d[1][0]
+            dst = d[1][1] if len(d[1]) > 1 else d[2].get("dtype")
+            if not isinstance(src, CSEVariable) or src.dtype not in FLOAT_DTYPES or dst not in FLOAT_DTYPES:
+                break
+            v = src
+        return v
+
+    def op_of(self, v, name: str):
+        """Operands of ``v`` if it was produced by op ``name`` (through float casts)."""
+        d = self.dag.get(str(self.resolve(v)))
+        return d[1] if d is not None and d[0] == name else None
+
+    def const_value(self, v):
+        d = self.dag.get(str(self.resolve(v)))
+        if d is not None and d[0] == "constant":
+            return d[1][0]
+        return v if isinstance(v, (int, float)) and not isinstance(v, bool) else None
+
+    def is_scalar(self, v) -> bool:
+        return not isinstance(v, CSEVariable) or str(v) in self.scalars
+
+    def is_float(self, v) -> bool:
+        return isinstance(v, CSEVariable) and v.dtype in FLOAT_DTYPES
+
+    def half_group(self) -> bool:
+        """True when the group reads or writes a 16-bit floating type (its results are
+        compared at that precision)."""
+        return self._narrowest_node_dtype() in (torch.float16, torch.bfloat16)
 
     # ------------------------------------------------------------------ policy hooks
     def should_use_persistent_reduction(self) -> bool:
@@ -172,20 +260,27 @@ class B200Kernel(SIMDKernel):
         return self._root("x"), self._root("r0_")
 
     def _outer_x_contiguous(self, exp: sympy.Expr) -> bool:
-        """x-vector contiguity of an access for every value of the reduced index."""
+        """x-vector contiguity of an access for every value of the reduced index, decided
+        from the structure of the index (no term may mix the kept and the reduced index)."""
         xr, rr = self._xr_roots()
-        rn = self._static_numel("r0_")
-        for r in sorted({0, rn - 1, rn // 2}):
-            e = exp.subs({rr.symbol(): r}) if rr is not None else exp
-            if not index_ir.is_vector_contiguous(e, xr.symbol(), self._outer_vec, self._static_numel("x")):
-                return False
-        return True
+        if self._static_numel("x") < self._outer_vec:
+            return False
+        if rr is None or rr.symbol() not in exp.free_symbols:
+            return index_ir.is_vector_contiguous(exp, xr.symbol(), self._outer_vec, self._static_numel("x"))
+        return index_ir.x_contiguous_for_all_r(exp, xr.symbol(), rr.symbol(), self._outer_vec)
 
     # ------------------------------------------------------------------ loads
+    def _refuse_fp64(self, name: str, dtype: torch.dtype) -> None:
+        if dtype == torch.float64 and not ixb_config.fp64_as_fp32:
+            raise UnsupportedByTemplates(
+                f"buffer {name} is float64: the B200 templates compute floating values in fp32 "
+                "(set IXB_FP64_AS_FP32=1 to accept that)")
+
     def load(self, name: str, index: sympy.Expr) -> CSEVariable:
         var = self.args.input(name)
         index = self.prepare_indexing(index)
         dtype = V.graph.get_dtype(name)
+        self._refuse_fp64(name, dtype)
         ctype = self.dtype_to_str(dtype)
         idx = self.index_to_str(index)
         indirect = self._is_indirect(index)
@@ -229,11 +324,35 @@ class B200Kernel(SIMDKernel):
                                                self._static_numel("r0_"))
         vector_row = has_r or indirect
         row_text = gather.replace("@M@", "rmask" if vector_row else "true")
+        const_member = None
         if stride == 1 and not masked:
             row_ptr = f"({var}) + ({G}lane0({idx}) - {G}lane0(r0_index))"
             row_text = f"c.load_row({row_ptr})"
-            if xr.symbol() in exp.free_symbols and row_ptr not in self._row_prefetch:
-                self._row_prefetch.append(row_ptr)     # streamed once per row: worth prefetching
+            cfg = self._row_cfg
+            n = cfg.elems_per_thread
+            narrow_ok = dtype in (torch.float32, torch.float16, torch.bfloat16) and \
+                config_bytes(dtype) >= config_bytes(self._narrowest_node_dtype())
+            if xr.symbol() not in exp.free_symbols:
+                # the same for every row (a per-column scale or shift): loaded and widened
+                # once per thread while registers allow
+                const_member = next((m for m, ptr, _ in self.consts if ptr == row_ptr), None)
+                if const_member is None and narrow_ok and (len(self.consts) + 1) * n <= MAX_CONST_REGS:
+                    const_member = f"k.k{len(self.consts)}"
+                    self.consts.append((const_member, row_ptr, n))
+                if const_member is not None:
+                    row_text = const_member
+            else:
+                if row_ptr not in self._row_prefetch:
+                    self._row_prefetch.append(row_ptr)     # streamed once per row: worth prefetching
+                aligned = index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
+                    self._static_numel("r0_") % cfg.vec == 0
+                if narrow_ok and aligned and cfg.team >= 32:
+                    member = next((m for m, _, ptr in self.staged if ptr == row_ptr), None)
+                    if member is None and len(self.staged) < MAX_STAGED:
+                        member = f"raw.s{len(self.staged)}"
+                        self.staged.append((member, ctype, row_ptr))
+                    if member is not None:
+                        row_text = f"c.template operand<STAGED, {ctype}>({member}, {row_ptr})"
         outer_text = gather.replace("@M@", "xmask")
         x_contig = False
         if not indirect and not masked and xr.symbol() in exp.free_symbols:
@@ -244,13 +363,20 @@ class B200Kernel(SIMDKernel):
         tag = self._placeholder("L", (name, idx, str(self._load_mask), other), row_text, outer_text,
                                 stride=stride, has_r=has_r, x_contig=x_contig, indirect=indirect, exp=exp,
                                 in_reduction=self.inside_reduction)
-        return self.cse.generate(self.compute, tag, dtype=val_dtype)
+        out = self.cse.generate(self.compute, tag, dtype=val_dtype)
+        self.dag.setdefault(out.name, ("load", (name, index), {}))
+        if not vector_row:
+            self.scalars.add(out.name)
+        if const_member is not None:
+            self.const_of[out.name] = const_member
+        return out
 
     # ------------------------------------------------------------------ stores
     def store(self, name: str, index: sympy.Expr, value: CSEVariable, mode=None) -> None:
         var = self.args.output(name)
         index = self.prepare_indexing(index)
         dtype = V.graph.get_dtype(name)
+        self._refuse_fp64(name, dtype)
         ctype = self.dtype_to_str(dtype)
         idx = self.index_to_str(index)
         if mode is not None:
@@ -273,7 +399,13 @@ class B200Kernel(SIMDKernel):
             stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
                                                self._static_numel("r0_"))
             if stride == 1:
-                row_text = f"c.store_row(({var}) + ({G}lane0({idx}) - {G}lane0(r0_index)), {value});"
+                row_ptr = f"({var}) + ({G}lane0({idx}) - {G}lane0(r0_index))"
+                row_text = f"c.store_row({row_ptr}, {value});"
+                cfg = self._row_cfg
+                if index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
+                        self._static_numel("r0_") % cfg.vec == 0 and dtype in FLOAT_DTYPES and \
+                        config_bytes(dtype) >= config_bytes(self._narrowest_node_dtype()):
+                    row_text = f"c.template put_row<STAGED>({row_ptr}, {value});"
         outer_text = f"{G}scatter({var}, {idx}, ixb::gen::op::logical_and(xmask, c.ty == 0), {value});"
         if not indirect and not has_r and self._outer_x_contiguous(exp):
             outer_text = (f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), c.ty == 0 ? nvalid : 0, "
@@ -292,6 +424,9 @@ class B200Kernel(SIMDKernel):
             self.inside_reduction = prior
 
     # ------------------------------------------------------------------ reductions
+    def _reduction_marker(self, tag: str) -> None:
+        self.compute.writeline(f"@B{tag[2:]}")  # marks where the reduction loop of the outer mapping ends
+
     def reduction(self, dtype, src_dtype, reduction_type, value):
         assert self.inside_reduction and self.is_row
         key = (src_dtype, reduction_type, value)
@@ -299,54 +434,199 @@ class B200Kernel(SIMDKernel):
             return self.cse.reduction_cache[key]
         if reduction_type == "welford_reduce" and not ixb_config.merged_welford:
             result = self.welford_reduce_fallback(dtype, value)
-        elif reduction_type == "online_softmax_reduce" and not ixb_config.merged_online_softmax:
+        elif reduction_type == "online_softmax_reduce" and not (ixb_config.merged_online_softmax
+                                                                and src_dtype in FLOAT_DTYPES):
             result = self.prepare_softmax_twopass_fallback(dtype, value)
         elif reduction_type == "welford_reduce":
             # (mean, m2, weight) from one exchange of merged partial statistics
             tag = self._placeholder("R", None, f"c.welford({value})", "", outer_ok=False)
-            self.compute.writeline(f"@B{tag[2:]}")
+            self._reduction_marker(tag)
             w = self.cse.generate(self.compute, tag, dtype=torch.float32)
             result = tuple(self.cse.generate(self.compute, f"{w}.{field}", dtype=torch.float32)
                            for field in ("mean", "m2", "weight"))
         elif reduction_type == "online_softmax_reduce":
-            # (row max, sum of exp(value - max)) from one exchange of rescaled partial sums
-            tag = self._placeholder("R", None, f"c.online_softmax({value})", "", outer_ok=False)
-            self.compute.writeline(f"@B{tag[2:]}")
-            ms = self.cse.generate(self.compute, tag, dtype=torch.float32)
-            result = tuple(self.cse.generate(self.compute, f"{ms}.{field}", dtype=torch.float32)
+            # (row max, sum of exp(value - max)) from one exchange of rescaled partial sums;
+            # the thread keeps its exponentials, and later row sums that are linear in them
+            # join the same exchange as riders (the text is completed in _substitute)
+            n = self._row_cfg.elems_per_thread
+            tag = self._placeholder("R", None, "", "", outer_ok=False, online=True, value=str(value),
+                                    riders_s=[], riders_p=[], n=n)
+            self._reduction_marker(tag)
+            ex = self.cse.generate(self.compute, tag, dtype=torch.float32)
+            self.dag.setdefault(ex.name, ("reduction", (reduction_type, value), {}))
+            result = tuple(self.cse.generate(self.compute, f"{ex}.{field}", dtype=torch.float32)
                            for field in ("max", "sum"))
+            info = dict(tag=tag, var=str(ex), max=str(result[0]), sum=str(result[1]), value=str(self.resolve(value)))
+            self.online[info["value"]] = info
         elif reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
             tag = self._placeholder("R", None, f"c.template reduce_arg<{is_max}>({value})", "", outer_ok=False)
-            self.compute.writeline(f"@B{tag[2:]}")
+            self._reduction_marker(tag)
             result = self.cse.generate(self.compute, tag, dtype=torch.int64)
         elif reduction_type == "any":
             tag = self._placeholder("R", None, f"c.reduce_any({value})", "", outer_ok=False)
-            self.compute.writeline(f"@B{tag[2:]}")
+            self._reduction_marker(tag)
             result = self.cse.generate(self.compute, tag, dtype=torch.bool)
         elif reduction_type in REDUCTION_OPS:
             op = REDUCTION_OPS[reduction_type]
             is_int = src_dtype in INT_DTYPES or src_dtype == torch.bool
-            row_text = f"c.template reduce<{op}>({value})"
-            outer_text = f"c.template combine<{op}>(acc)"
-            if is_int:
-                # exact up to 2^24; integer reductions beyond that need an integer exchange
-                row_text = f"ixb::gen::op::to_int({row_text})"
-                outer_text = f"ixb::gen::op::to_int({outer_text})"
-            tag = self._placeholder("R", None, row_text, outer_text, outer_ok=True, op=op,
-                                    value=str(value), rtype=reduction_type)
-            self.compute.writeline(f"@B{tag[2:]}")  # marks where the reduction loop ends
-            result = self.cse.generate(self.compute, tag,
-                                       dtype=torch.int64 if is_int else torch.float32)
+            hoisted = None if is_int or reduction_type != "sum" else self._sum_from_earlier_exchange(value)
+            if hoisted is not None:
+                result = self.cse.generate(self.compute, hoisted, dtype=torch.float32)
+            else:
+                row_text = f"c.template reduce<{op}>({value})"
+                outer_text = f"c.template combine<{op}>(acc)"
+                if reduction_type == "sum" and not is_int:
+                    factors = self.op_of(value, "mul")
+                    if factors is not None and all(self.is_float(f) for f in factors):
+                        row_text = f"c.reduce_dot({factors[0]}, {factors[1]})"
+                if is_int:
+                    # 64-bit integer accumulation and exchange: exact (the float path would
+                    # round sums beyond 2^24)
+                    iop = INT_REDUCTION_OPS[reduction_type]
+                    row_text = f"c.template reduce_int<typename Ctx::{iop}>({value})"
+                    outer_text = f"c.template combine_int<typename Ctx::{iop}>(acc)"
+                tag = self._placeholder("R", None, row_text, outer_text, outer_ok=True, op=op,
+                                        value=str(value), rtype=reduction_type, is_int=is_int)
+                self._reduction_marker(tag)
+                result = self.cse.generate(self.compute, tag,
+                                           dtype=torch.int64 if is_int else torch.float32)
         else:
             raise UnsupportedByTemplates(f"reduction type {reduction_type}")
+        for r in (result if isinstance(result, tuple) else (result,)):
+            if isinstance(r, CSEVariable):
+                self.scalars.add(r.name)
+                self.dag.setdefault(r.name, ("reduction", (reduction_type, value), {}))
         self.cse.reduction_cache[key] = result
         return result
 
+    # ---- sums that ride in the online-softmax exchange -----------------------------------
+    # With e = exp(v - max(v)) and S = sum(e) coming out of one exchange, a later
+    #   sum(e / S * g + v)  ==  sum(e * g) / S + sum(v)
+    # needs no exchange of its own: sum(e * g) and sum(v) can be accumulated per thread before
+    # the maximum is known and folded together with S.  A value qualifies when it is a linear
+    # combination, with row-scalar coefficients, of (a) e times a vector that does not depend
+    # on the exchange and (b) vectors that do not depend on it.
+    def _depends_on(self, v, ex, seen=None) -> bool:
+        if not isinstance(v, CSEVariable):
+            return False
+        name = str(v)
+        if name in (ex["max"], ex["sum"], ex["var"]) or name in self.online_exp:
+            return True
+        d = self.dag.get(name)
+        if d is None:
+            return True          # unknown origin: assume the worst
+        if d[0] in ("load", "constant", "index_expr"):
+            return False
+        if d[0] == "reduction":
+            return True
+        return any(self._depends_on(a, ex) for a in d[1])
+
+    def _early_text(self, v, ex):
+        """Text that names the float vector ``v`` at the point of the exchange ``ex``, or None
+        if ``v`` is only defined later."""
+        v = self.resolve(v)
+        name = str(v)
+        if name in self.const_of:
+            return self.const_of[name]
+        order = list(self.dag)
+        if name in self.dag and ex["var"] in self.dag and order.index(name) < order.index(ex["var"]):
+            return name if not self.is_scalar(v) else None
+        return None
+
+    def _linear_form(self, v, ex, depth=0):
+        """[(coefficient text or None, 'e' | 'p', vector text or None)] or None."""
+        OPN = "ixb::gen::op::"
+        v = self.resolve(v)
+        name = str(v)
+        if depth > 12 or not self.is_float(v):
+            return None
+        if self.online_exp.get(name) is ex:
+            return [(None, "e", None)]
+        if not self._depends_on(v, ex):
+            if self.is_scalar(v):
+                return None
+            t = self._early_text(v, ex)
+            return [(None, "p", t)] if t is not None else None
+        d = self.dag.get(name)
+        if d is None:
+            return None
+        opn, args = d[0], d[1]
+
+        def scaled(form, factor, divide=False):
+            out = []
+            for coef, kind, w in form:
+                if divide:
+                    c = f"{OPN}truediv({coef if coef is not None else '1.0f'}, {factor})"
+                else:
+                    c = str(factor) if coef is None else f"{OPN}mul({coef}, {factor})"
+                out.append((c, kind, w))
+            return out
+
+        if opn == "mul" and len(args) == 2:
+            for a, b in ((args[0], args[1]), (args[1], args[0])):
+                fa = self._linear_form(a, ex, depth + 1)
+                if fa is None:
+                    continue
+                if self.is_scalar(b) and (isinstance(b, CSEVariable) or isinstance(b, (int, float))):
+                    return scaled(fa, b)
+                if self.is_float(b) and not self._depends_on(b, ex):
+                    wt = self._early_text(b, ex)
+                    if wt is None:
+                        return None
+                    return [(coef, kind, wt if w is None else f"{OPN}mul({w}, {wt})") for coef, kind, w in fa]
+            return None
+        if opn == "truediv" and len(args) == 2 and self.is_scalar(args[1]):
+            fa = self._linear_form(args[0], ex, depth + 1)
+            return None if fa is None else scaled(fa, args[1], divide=True)
+        if opn in ("add", "sub") and len(args) == 2:
+            fa = self._linear_form(args[0], ex, depth + 1)
+            fb = self._linear_form(args[1], ex, depth + 1)
+            if fa is None or fb is None:
+                return None
+            if opn == "sub":
+                fb = [(f"{OPN}neg({c if c is not None else '1.0f'})", kind, w) for c, kind, w in fb]
+            return fa + fb
+        return None
+
+    def _sum_from_earlier_exchange(self, value):
+        if not self.online or not ixb_config.merged_online_softmax:
+            return None
+        ex = list(self.online.values())[-1]
+        form = self._linear_form(value, ex)
+        if form is None:
+            return None
+        ph = self._ph[ex["tag"]]
+        rs, rp = list(ph["riders_s"]), list(ph["riders_p"])
+        terms = []
+        for coef, kind, w in form:
+            if kind == "e" and w is None:
+                total = ex["sum"]
+            elif kind == "e":
+                if w not in rs:
+                    rs.append(w)
+                total = f"{ex['var']}.scaled[{rs.index(w)}]"
+            else:
+                if w is None:
+                    return None
+                if w not in rp:
+                    rp.append(w)
+                total = f"{ex['var']}.plain[{rp.index(w)}]"
+            terms.append(total if coef is None else f"ixb::gen::op::mul({coef}, {total})")
+        if len(rs) + len(rp) > 2:
+            return None
+        ph["riders_s"], ph["riders_p"] = rs, rp
+        text = terms[0]
+        for t in terms[1:]:
+            text = f"ixb::gen::op::add({text}, {t})"
+        return text
+
     # ------------------------------------------------------------------ bounds checks
     def check_bounds(self, expr, size, lower, upper) -> None:
-        # indirect indices are wrapped by Inductor's lowering; out-of-range indices are the
-        # caller's error as in eager mode, they are not trapped on the device
+        # Negative indices are wrapped by Inductor's lowering.  Range checks are made where the
+        # index is formed (B200Overrides.indirect_indexing) in modules generated with
+        # config.debug_bounds; otherwise an out-of-range index is the caller's error, as in
+        # eager mode.  Nothing is trapped on the device either way.
         return
 
     # ------------------------------------------------------------------ assembling
@@ -422,6 +702,10 @@ class B200Kernel(SIMDKernel):
 
     def _substitute(self, text: str, outer: bool) -> str:
         for tag, v in self._ph.items():
+            if v.get("online") and not outer:
+                rs, rp = v["riders_s"], v["riders_p"]
+                v["row"] = (f"c.template online_softmax<{len(rs)}, {len(rp)}>({v['value']}, "
+                            f"{G}refs<kN>({', '.join(rs)}), {G}refs<kN>({', '.join(rp)}))")
             text = text.replace(tag, v["outer"] if outer else v["row"])
         return text
 
@@ -435,12 +719,20 @@ class B200Kernel(SIMDKernel):
         self.mapping = "outer" if outer else ("row" if self.is_row else "pointwise")
 
         src = IndentedBuffer()
+        if self.checked_indices:
+            src.writeline("#define IXB_DEBUG_BOUNDS 1")
         src.writeline('#include "ixb/gen.cuh"')
         if self.is_row and not outer:
-            # register bound; the module loader rebuilds with a smaller value on spills
-            src.writeline("#ifndef IXB_GEN_MIN_CTAS")
-            src.writeline(f"#define IXB_GEN_MIN_CTAS {self._row_cfg.min_ctas}")
-            src.writeline("#endif")
+            # The launch shape is a set of macros so that the module loader can build the
+            # same body in other shapes (-D...) and keep the one that measures fastest;
+            # IXB_GEN_MIN_CTAS bounds the registers and is relaxed by the loader on spills.
+            cfg = self._row_cfg
+            for macro, val in (("IXB_GEN_MIN_CTAS", cfg.min_ctas), ("IXB_ROW_TEAM", cfg.team),
+                               ("IXB_ROW_TEAMS", cfg.teams), ("IXB_ROW_VPT", cfg.vpt),
+                               ("IXB_ROW_PF", cfg.prefetch)):
+                src.writeline(f"#ifndef {macro}")
+                src.writeline(f"#define {macro} {val}")
+                src.writeline("#endif")
         src.writeline("namespace {")
         src.writeline("using namespace ixb;")
         src.writeline("struct Body {")
@@ -452,12 +744,13 @@ class B200Kernel(SIMDKernel):
                 marker = red_tag.replace("@R", "@B")
                 head, _, tail = body_text.partition(marker)
                 rnumel = self._static_numel("r0_")
+                conv = "to_int" if red.get("is_int") else "to_float"
                 acc_line = {
-                    "sum": "acc = ixb::gen::op::add(acc, ixb::gen::op::to_float({v}));",
-                    "prod": "acc = ixb::gen::op::mul(acc, ixb::gen::op::to_float({v}));",
-                    "max": "acc = ixb::gen::op::maximum(acc, ixb::gen::op::to_float({v}));",
-                    "min": "acc = ixb::gen::op::minimum(acc, ixb::gen::op::to_float({v}));",
-                }[red["rtype"]].format(v=red["value"])
+                    "sum": "acc = ixb::gen::op::add(acc, ixb::gen::op::{c}({v}));",
+                    "prod": "acc = ixb::gen::op::mul(acc, ixb::gen::op::{c}({v}));",
+                    "max": "acc = ixb::gen::op::maximum(acc, ixb::gen::op::{c}({v}));",
+                    "min": "acc = ixb::gen::op::minimum(acc, ixb::gen::op::{c}({v}));",
+                }[red["rtype"]].format(v=red["value"], c=conv)
                 src.writeline(f"static constexpr int kVec = {self._outer_vec};")
                 src.writeline("template <bool FAST, class Ctx>")
                 src.writeline("__device__ __forceinline__ void tile(Ctx& c, const long long xbase, const int nvalid) const {")
@@ -465,7 +758,11 @@ class B200Kernel(SIMDKernel):
                     src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
                     src.writeline("const auto xmask = xindex < (xbase + nvalid);")
                     src.splice(x_idx)
-                    src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
+                    if red.get("is_int"):
+                        iop = INT_REDUCTION_OPS[red["rtype"]]
+                        src.writeline(f"auto acc = Ctx::template splat_int<kVec>(Ctx::{iop}::id());")
+                    else:
+                        src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
                     src.writeline("#pragma unroll 8")  # independent loads of eight steps in flight
                     src.writeline(f"for (long long r0_index = c.ty; r0_index < {rnumel}LL; r0_index += Ctx::kTY) {{")
                     with src.indent():
@@ -478,8 +775,44 @@ class B200Kernel(SIMDKernel):
             elif self.is_row:
                 import re
 
+                cfg = self._row_cfg
+                src.writeline(f"static constexpr int kN = IXB_ROW_VPT * {cfg.vec};   // elements per thread")
+                src.writeline("struct Consts {")
+                with src.indent():
+                    for member, _, _ in self.consts:
+                        src.writeline(f"{G}vf<kN> {member[2:]};")
+                src.writeline("};")
+                src.writeline("struct Raw {")
+                with src.indent():
+                    for member, ctype, _ in self.staged:
+                        src.writeline(f"{G}RawRow<{ctype}, IXB_ROW_VPT, {cfg.vec}> {member[4:]};")
+                src.writeline("};")
+                # operands that are the same for every row: once per thread
                 src.writeline("template <class Ctx>")
-                src.writeline("__device__ __forceinline__ void row(Ctx& c, const long long xindex) const {")
+                src.writeline("__device__ __forceinline__ void init(Ctx& c, Consts& k) const {")
+                with src.indent():
+                    if self.consts:
+                        src.writeline("const long long xindex = 0;")
+                        src.writeline("const auto r0_index = c.rindex();")
+                        src.splice(x_idx)
+                        src.splice(r_idx)
+                        for member, ptr, _ in self.consts:
+                            src.writeline(f"{member} = c.load_row({ptr});")
+                src.writeline("}")
+                # raw vectors of the streamed operands of one row (requested a row ahead)
+                src.writeline("template <class Ctx>")
+                src.writeline("__device__ __forceinline__ void fetch(Ctx& c, const long long xindex, Raw& raw) const {")
+                with src.indent():
+                    if self.staged:
+                        src.writeline("const auto r0_index = c.rindex();")
+                        src.splice(x_idx)
+                        src.splice(r_idx)
+                        for member, _, ptr in self.staged:
+                            src.writeline(f"c.fetch_row({ptr}, {member});")
+                src.writeline("}")
+                src.writeline("template <bool STAGED, class Ctx>")
+                src.writeline("__device__ __forceinline__ void row(Ctx& c, const Consts& k, const long long xindex, "
+                              "const Raw& raw) const {")
                 with src.indent():
                     src.writeline("const auto r0_index = c.rindex();")
                     src.writeline("const auto rmask = c.rmask();")
@@ -521,19 +854,35 @@ class B200Kernel(SIMDKernel):
             elif self.is_row:
                 cfg = self._row_cfg
                 rnumel = self._static_numel("r0_")
-                rt = {4: "float", 8: "ixb::bf16"}[cfg.vec]
+                # the type that fixes how many elements one 128-bit vector of the row holds
                 narrow = self._narrowest_node_dtype()
-                if cfg.vec == 8 and narrow == torch.float16:
-                    rt = "ixb::f16"
-                full = "true" if cfg.capacity == rnumel else "false"   # no ragged tail to test for
-                src.writeline(f"return {G}launch_row_gen<Body, {rt}, {cfg.team}, {cfg.teams}, {cfg.vpt}, "
-                              f"IXB_GEN_MIN_CTAS, {cfg.prefetch}, {full}>(b, {xnumel}LL, {rnumel}, stream);")
+                rt = {torch.float32: "float", torch.bfloat16: "ixb::bf16", torch.float16: "ixb::f16"}.get(
+                    narrow, f"ixb::Lanes<{cfg.vec}>")
+                nptr = len([a for a in assigns if 'ptrs[' in a])
+                # FULL: the row fills every vector of the team, no ragged tail to test for
+                src.writeline(f"constexpr bool kFull = IXB_ROW_TEAM * IXB_ROW_VPT * {cfg.vec} == {rnumel};")
+                src.writeline(f"return {G}launch_row_gen<Body, {rt}, IXB_ROW_TEAM, IXB_ROW_TEAMS, IXB_ROW_VPT, "
+                              f"IXB_GEN_MIN_CTAS, IXB_ROW_PF, kFull>(b, {xnumel}LL, {rnumel}, stream, "
+                              f"{G}pointers_aligned(ptrs, {nptr}));")
             else:
                 src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream, "
                               f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
         src.writeline("}")
+        if self.checked_indices:
+            src.writeline('extern "C" int ixb_gen_bounds(unsigned long long* out) { '
+                          'return ixb::gen::read_bounds_status(out); }')
         text = src.getvalue()
-        return f"ixb_load_kernel('''\n{text}''', family={self.mapping!r})"
+        meta = f"family={self.mapping!r}"
+        if self.checked_indices:
+            meta += ", bounds=True"
+        if self.mapping == "row":
+            cfg = self._row_cfg
+            inplace = bool(self.args.inplace_buffers)
+            shapes = split_tiling.row_candidates(self._static_numel("r0_"), cfg, rows=xnumel)
+            meta += (f", tune=dict(default={(cfg.team, cfg.teams, cfg.vpt, cfg.min_ctas, cfg.prefetch)!r}, "
+                     f"candidates={shapes!r}, rows={xnumel}, row_bytes={self._static_numel('r0_') * config_bytes(self._narrowest_node_dtype())}, "
+                     f"idempotent={not inplace!r})")
+        return f"ixb_load_kernel('''\n{text}''', {meta})"
 
     def call_kernel(self, name: str, node: Any = None, deallocate_ws: bool = True) -> None:
         wrapper = V.graph.wrapper_code

@@ -146,6 +146,20 @@ class B200Overrides(OpOverrides):
         return str(var)
 
     @staticmethod
+    def indirect_indexing(var, size, check=True, wrap_neg=True):
+        from torch._inductor.utils import sympy_index_symbol
+
+        from .. import config as ixb_config
+
+        if ixb_config.debug_bounds and check and hasattr(V.kernel, "checked_indices"):
+            # debug build: count a violation, keep the access inside the buffer
+            bound = V.kernel.sexpr(V.kernel.rename_indexing(sympy.sympify(size)))
+            var = V.kernel.cse.generate(V.kernel.compute, f"ixb::gen::checked_index({var}, {bound})",
+                                        dtype=torch.int64)
+            V.kernel.checked_indices += 1
+        return sympy_index_symbol(str(var))
+
+    @staticmethod
     def masked(mask, body, other):
         with V.kernel.mask_loads(mask, other) as new_mask:
             result = body()
@@ -184,6 +198,117 @@ class B200Overrides(OpOverrides):
         raise NotImplementedError("random number ops are not instantiable from the B200 templates")
 
 
+def _kernel():
+    k = V.kernel
+    return k if hasattr(k, "dag") else None
+
+
+def _floats(k, *vals) -> bool:
+    return all(k.is_float(v) or isinstance(v, float) for v in vals) and any(k.is_float(v) for v in vals)
+
+
+class _Peephole:
+    """Rewrites applied while the op text is printed.  They do what a compiler does for
+    scalar code but cannot do across the packed-pair instructions the vector ops are made
+    of: contraction of a*b+c into one fused multiply-add, folding of row-scalar factors into
+    one scalar so that a vector is multiplied once, exp(a - rowmax) from the exponentials the
+    online-softmax exchange already holds, and the decomposed exact GELU as one call."""
+
+    @staticmethod
+    def add(a, b):
+        k = _kernel()
+        if k is not None and _floats(k, a, b):
+            for p, q in ((a, b), (b, a)):
+                m = k.op_of(p, "mul")
+                if m is not None and _floats(k, *m):
+                    return f"{OP}fma({m[0]}, {m[1]}, {q})"
+        return f"{OP}add({a}, {b})"
+
+    @staticmethod
+    def sub(a, b):
+        k = _kernel()
+        if k is not None and _floats(k, a, b):
+            m = k.op_of(a, "mul")
+            if m is not None and _floats(k, *m) and k.is_scalar(b):
+                return f"{OP}fma({m[0]}, {m[1]}, {OP}neg({b}))"
+        return f"{OP}sub({a}, {b})"
+
+    @staticmethod
+    def _gelu(k, a, b):
+        """a == v * 0.5 and b == erf(v * sqrt(1/2)) + 1  ->  v"""
+        ma, sb = k.op_of(a, "mul"), k.op_of(b, "add")
+        if ma is None or sb is None:
+            return None
+        for v, half in ((ma[0], ma[1]), (ma[1], ma[0])):
+            if k.const_value(half) != 0.5:
+                continue
+            for e, one in ((sb[0], sb[1]), (sb[1], sb[0])):
+                if k.const_value(one) != 1.0:
+                    continue
+                inner = k.op_of(e, "erf")
+                me = k.op_of(inner[0], "mul") if inner is not None else None
+                if me is None:
+                    continue
+                for v2, c in ((me[0], me[1]), (me[1], me[0])):
+                    cv = k.const_value(c)
+                    if cv is not None and abs(cv - 0.7071067811865476) < 1e-12 and \
+                            str(k.resolve(v2)) == str(k.resolve(v)):
+                        return v
+        return None
+
+    @staticmethod
+    def mul(a, b):
+        k = _kernel()
+        if k is not None and _floats(k, a, b):
+            for p, q in ((a, b), (b, a)):
+                v = _Peephole._gelu(k, p, q)
+                if v is not None:
+                    k.pending_dag = ("gelu_erf", (v,), {})
+                    return f"{OP}gelu_erf({v})"
+            # (vector * s1) * s2 -> vector * (s1 * s2); (vector / s1) * s2 -> vector * (s2 / s1)
+            for p, q in ((a, b), (b, a)):
+                if not k.is_scalar(q) or k.is_scalar(p):
+                    continue
+                m = k.op_of(p, "mul")
+                if m is not None and _floats(k, *m):
+                    for v, s1 in ((m[0], m[1]), (m[1], m[0])):
+                        if k.is_scalar(s1) and not k.is_scalar(v):
+                            return f"{OP}mul({v}, {OP}mul({s1}, {q}))"
+                d = k.op_of(p, "truediv")
+                if d is not None and _floats(k, *d) and k.is_scalar(d[1]) and not k.is_scalar(d[0]):
+                    return f"{OP}mul({d[0]}, {OP}truediv({q}, {d[1]}))"
+        return f"{OP}mul({a}, {b})"
+
+    @staticmethod
+    def truediv(a, b):
+        k = _kernel()
+        if k is not None and _floats(k, a, b) and k.is_scalar(b) and not k.is_scalar(a):
+            ex = k.online_exp.get(str(k.resolve(a)))
+            if ex is not None:
+                # exp(v - max) / s: the thread's exponentials times one scalar
+                return f"{OP}mul({ex['var']}.e, {OP}truediv({ex['var']}.r, {b}))"
+            m = k.op_of(a, "mul")
+            if m is not None and _floats(k, *m):
+                for v, s1 in ((m[0], m[1]), (m[1], m[0])):
+                    if k.is_scalar(s1) and not k.is_scalar(v):
+                        return f"{OP}mul({v}, {OP}truediv({s1}, {b}))"
+        return f"{OP}truediv({a}, {b})"
+
+    @staticmethod
+    def exp(a):
+        k = _kernel()
+        if k is not None and k.is_float(a):
+            s = k.op_of(a, "sub")
+            if s is not None and _floats(k, *s):
+                ex = k.online.get(str(k.resolve(s[0])))
+                if ex is not None and str(s[1]) == ex["max"]:
+                    k.pending_online_exp = ex
+                    return f"{OP}mul({ex['var']}.e, {ex['var']}.r)"
+                if k.is_scalar(s[1]) and not k.is_scalar(s[0]) and k.half_group():
+                    return f"{OP}exp_sub({s[0]}, {s[1]})"
+        return f"{OP}exp({a})"
+
+
 for _name in ["exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "rsqrt", "sin", "cos",
               "tan", "asin", "acos", "atan", "sinh", "cosh", "tanh", "erf", "erfc", "lgamma", "floor",
               "ceil", "trunc", "round", "reciprocal", "sigmoid", "abs", "neg", "square", "relu",
@@ -192,9 +317,11 @@ for _name in ["exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "
               "remainder", "logical_and", "logical_or", "logical_xor", "logical_not", "eq", "ne",
               "lt", "le", "gt", "ge", "where"]:
     setattr(B200Overrides, _name, _call(_name))
+for _name in ["add", "sub", "mul", "truediv", "exp"]:
+    setattr(B200Overrides, _name, staticmethod(getattr(_Peephole, _name)))
 B200Overrides.mod = _call("mod")
 B200Overrides.int_truediv = _call("truediv")
-B200Overrides.libdevice_exp = _call("exp")
+B200Overrides.libdevice_exp = staticmethod(_Peephole.exp)
 B200Overrides.libdevice_sqrt = _call("sqrt")
 B200Overrides.libdevice_log = _call("log")
 B200Overrides.libdevice_sigmoid = _call("sigmoid")

@@ -91,6 +91,36 @@ def choose_row_config(rnumel: int, dtype: torch.dtype, rows: Optional[int] = Non
                      prefetch=2 if streamed and row_bytes >= 2048 else 0)
 
 
+def row_candidates(rnumel: int, chosen: RowConfig, rows: Optional[int] = None):
+    """Launch shapes worth measuring for a generated row kernel besides ``chosen``:
+    ``(team, teams, vpt, min_ctas, prefetch)`` tuples.  One, two and four vectors per
+    thread over the matching power-of-two team, CTAs of 128 or 256 threads (or one team),
+    registers bounded for 512, 768 or 1024 resident threads per SM.  Shapes that keep the
+    chosen number of vectors per thread come first; the module loader builds the first few
+    and keeps the one with the highest measured bandwidth (``codegen/jit.py``)."""
+    vec = chosen.vec
+    nvec = -(-rnumel // vec)
+    out = []
+    if chosen.team < 32:
+        return out                        # rows of a few vectors: the static choice stands
+    for vpt in sorted((1, 2, 4), key=lambda v: (v != chosen.vpt, abs(v - chosen.vpt))):
+        team = 32
+        while team < MAX_TEAM and team * vpt < nvec:
+            team *= 2
+        if team * vpt < nvec or (vpt > 1 and team * (vpt // 2) >= nvec):
+            continue                      # does not cover the row / leaves idle vectors
+        for cta in (128, 256):
+            teams = max(1, cta // team)
+            threads = team * teams
+            for resident in (1024, 512, 768):
+                min_ctas = max(1, resident // threads)
+                shape = (team, teams, vpt, min_ctas, chosen.prefetch)
+                if shape not in out:
+                    out.append(shape)
+    default = (chosen.team, chosen.teams, chosen.vpt, chosen.min_ctas, chosen.prefetch)
+    return [s for s in out if s != default]
+
+
 def choose_pointwise_vec(dtypes: Iterable[torch.dtype]) -> int:
     """Elements per thread of a pointwise kernel: one 128-bit access of the narrowest
     operand, at least 4."""

@@ -1,4 +1,5 @@
 // C-ABI entry point of the GATHER family.
+#include <atomic>
 #include "host.h"
 #include "ixb/gather.cuh"
 
@@ -27,14 +28,15 @@ int gather_t(const void* table, const void* idx, void* out, int64_t n_rows, int6
     // vectors.  A grid of a few waves would leave the last wave partly empty.
     constexpr int kUnroll = 2;
     auto kern = ixb::gather_rows_kernel<IdxT, kUnroll, WRAP>;
-    static int resident[64] = {};
+    static std::atomic<int> resident[64];   // per device; several host threads may ask at once
     int devid = 0;
     cudaGetDevice(&devid);
-    int& occ = resident[devid & 63];
+    int occ = resident[devid & 63].load(std::memory_order_acquire);
     if (occ == 0) {
       int n = 0;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, 0) != cudaSuccess || n < 1) n = 1;
       occ = n;
+      resident[devid & 63].store(n, std::memory_order_release);
     }
     const long long vecs = (long long)m * vpr;
     long long grid = (vecs + 256LL * kUnroll - 1) / (256LL * kUnroll);

@@ -96,14 +96,16 @@ extern "C" int ixb_outer_reduce_static(int dtype, int kind, const void* x, void*
   if (outer < 0 || R <= 0 || inner < 0 || rsplit < 1) return IXB_ERR_ARG;
   if (outer == 0 || inner == 0) return IXB_OK;
   if (x == nullptr || out == nullptr) return IXB_ERR_ARG;
-  const int es = ixb_host::elem_size(dtype);
   if (dtype != IXB_F32 && dtype != IXB_F16 && dtype != IXB_BF16) return IXB_ERR_DTYPE;
+  const int es = ixb_host::elem_size(dtype);
   if (inner % (16 / es) != 0 || !ixb_host::aligned16(x)) return IXB_ERR_ALIGN;
   if (rsplit > R) rsplit = (int)R;
-  // the partials must fit the fixed array: refuse anything larger, never spill over
-  const unsigned long long need =
-      (unsigned long long)outer * (unsigned long long)inner * (unsigned long long)rsplit;
-  if (need > kStaticScratchFloats) return IXB_ERR_SCRATCH;
+  // the partials must fit the fixed array: refuse anything larger, never spill over.  Each
+  // factor is checked against what is left of the capacity, so the product cannot wrap.
+  const unsigned long long cap = kStaticScratchFloats;
+  if ((unsigned long long)outer > cap || (unsigned long long)inner > cap / (unsigned long long)outer ||
+      (unsigned long long)rsplit > cap / ((unsigned long long)outer * (unsigned long long)inner))
+    return IXB_ERR_SCRATCH;
   float* scratch = nullptr;
   if (int st = scratch_for_current_device(&scratch)) return st;
   cudaStream_t s = (cudaStream_t)stream;

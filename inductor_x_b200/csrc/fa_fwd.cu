@@ -19,6 +19,7 @@
 // `status` and lets the CTA drain and exit.
 //
 // TMEM columns: [0,128) S/P of A, [128,256) S/P of B, [256,384) O of A, [384,512) O of B.
+#include <atomic>
 #include "host.h"
 #include "ixb/tcgen05.cuh"
 
@@ -57,16 +58,6 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_bf16) 
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
-
-// Development aid (never defined in the shipped build): CTA (0, 0) writes SM clock stamps
-// of its hand-offs into the buffer passed as `lse`.
-#ifdef IXB_FA_TIMING
-#define IXB_FA_STAMP(cond, slot)                                                       \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && (cond))                                    \
-    reinterpret_cast<long long*>(p.lse)[slot] = clock64();
-#else
-#define IXB_FA_STAMP(cond, slot)
-#endif
 
 template <bool IS_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -222,7 +213,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           // every wait of this tile's step comes first, so that its sixteen MMAs go to the
           // tensor core back to back and its queue does not drain in between
           const bool do_pv = j < n_kv_t[t], do_qk = j + 1 < n_kv_t[t];
-          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 0);
           if (do_pv) {
             ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
             if (v_seen != j) {  // a stage is waited for once, not once per tile
@@ -235,20 +225,17 @@ __global__ void __launch_bounds__(kThreads, 1)
             k_seen = j + 1;
           }
           if (!ok) break;
-          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 2);
           tc::fence_after_sync();
           if (do_pv) {
             issue_pv(t, s, j > 0);
             tc::mma_commit(&pv_done[t]);
           }
-          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 3);
           if (do_qk) {
             // P_t(j) has been consumed by the MMAs just issued (the tensor core runs
             // them in order), so tile t's buffer can take S_t(j+1)
             issue_qk(t, s1);
             tc::mma_commit(&s_full[t]);
           }
-          IXB_FA_STAMP(j < 32, 256 + (j * 2 + t) * 6 + 5);
         }
         if (!ok) break;
         tc::mma_commit(&v_empty[s]);
@@ -278,7 +265,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc::fence_after_sync();
-      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 0);
       const int col0 = j * BN;
       const bool edge = (col0 + BN > p.Sk) || (p.causal && (col0 + BN - 1 > qt0 + diag));
       // last visible key of this row, relative to the tile
@@ -306,7 +292,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             mx = max3(mx, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
         }
       }
-      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 1);
       mx *= p.scale_log2;  // scale > 0: scaling commutes with the maximum
       // lazy rescale: move the reference maximum only when it would grow by > 2^8
       const bool grow = mx > m_used + kRescaleThreshold;  // also true for the first tile
@@ -334,7 +319,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         m_used = m_new;
       }
-      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 2);
       // ---- pass 2: P = exp2(s * scale - m_used); the next 32 columns are requested
       // before the current 32 are processed so the TMEM latency overlaps the arithmetic
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
@@ -370,7 +354,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       l += sum2.x + sum2.y;
       tc::tmem_wait_st();
       tc::fence_before_sync();
-      IXB_FA_STAMP(row == 0 && j < 32, (t * 32 + j) * 4 + 3);
       tc::mbar_arrive(&p_full[t]);
     }
 
@@ -401,12 +384,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-#ifndef IXB_FA_TIMING
         if (live && p.lse != nullptr) {
           const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.69314718055994530942f : -INFINITY;
           p.lse[((long long)b * p.H + h) * p.Sq + qi] = lse;
         }
-#endif
       }
     } else {
       failed = 1;
@@ -501,8 +482,16 @@ extern "C" int ixb_fa_fwd(int dtype, const void* q, const void* k, const void* v
   if (!(scale > 0.f)) return IXB_ERR_ARG;  // the row maximum is taken before scaling
   const dim3 grid((Sq + BM * NQ - 1) / (BM * NQ), B * H);
   auto kern = is_bf16 ? fa_fwd_kernel<true> : fa_fwd_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-  if (e != cudaSuccess) return ixb_host::cuda_status(e);
+  // the shared-memory opt-in is a property of (kernel, device): set once per device
+  static std::atomic<bool> configured[2][64];
+  int devid = 0;
+  cudaGetDevice(&devid);
+  std::atomic<bool>& done = configured[is_bf16][devid & 63];
+  if (!done.load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return ixb_host::cuda_status(e);
+    done.store(true, std::memory_order_release);
+  }
   kern<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(mq, mk, mv, p);
   return ixb_host::cuda_status(cudaGetLastError());
 }

@@ -40,6 +40,14 @@ template <> struct Elem<bf16> {
   static __device__ __forceinline__ bf16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
+// Layout-only element type: KV elements per thread vector, for rows of a storage type the
+// prebuilt bodies never load themselves (integers, booleans); generated bodies bring their
+// own typed loads and use the row context only for the column arithmetic.
+template <int KV> struct Lanes {};
+template <int KV> struct Elem<Lanes<KV>> {
+  static constexpr int kVec = KV;
+};
+
 // 128-bit global access.  Inputs that are read once stream through L1 without
 // allocating; outputs use a streaming store so they do not evict reusable lines.
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {

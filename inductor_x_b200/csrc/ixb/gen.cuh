@@ -15,6 +15,8 @@
 // pointwise_npu_index / persistent_reduction_npu_index / reduction_npu_index
 // (inductor_x/npu_triton_heuristics.py:545-611).
 #pragma once
+#include <atomic>
+
 #include "gen_ops.cuh"
 #include "row.cuh"
 
@@ -149,7 +151,7 @@ __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(
   if constexpr ((N % kPer) == 0 && (sizeof(T) == 2 || sizeof(T) == 4) && std::is_same<V, float>::value) {
     if (FAST || (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0)) {
 #pragma unroll
-      for (int c = 0; c < N / kPer; ++c) unpack<T>(ldg_keep(p + c * kPer), &r.v[c * kPer]);
+      for (int c = 0; c < N / kPer; ++c) unpack<T>(ldg_keep(p + c * kPer), &r.v[c * kPer]);  // may be re-read: keep in L1
       return r;
     }
   }
@@ -196,6 +198,34 @@ __device__ __forceinline__ auto igather(const T* p, const I& idx, const M& mask,
     return gather(p, idx, mask, other);
   }
 }
+
+// ---- bounds check of indirect indices (debug builds) ---------------------------------------
+// A module generated with IXB_DEBUG_BOUNDS checks every data-dependent index against the
+// extent it addresses (the reference asserts them on the device,
+// inductor_x/codegen/triton.py:1666-1710).  A violation is counted, one offending value is
+// kept, and the index is replaced by 0 so that the access stays inside the buffer; the
+// launcher reads the two words after the launch and raises on the host.  Nothing traps.
+#ifdef IXB_DEBUG_BOUNDS
+static __device__ unsigned long long g_bounds_status[2];  // [violations, one offending index]
+__device__ __forceinline__ long long checked_one(long long x, long long size) {
+  if (x < 0 || x >= size) {
+    atomicAdd(&g_bounds_status[0], 1ull);
+    atomicExch(&g_bounds_status[1], (unsigned long long)x);
+    return 0;
+  }
+  return x;
+}
+template <class I> __device__ __forceinline__ auto checked_index(const I& idx, long long size) {
+  return map1<typename ires<rank<I>::n>::type>([size](long long x) { return checked_one(x, size); }, idx);
+}
+// host: fetch and clear the status words of this module (synchronises the device)
+inline int read_bounds_status(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_bounds_status, 2 * sizeof(unsigned long long));
+  if (e != cudaSuccess) return (int)e;
+  const unsigned long long zero[2] = {0ull, 0ull};
+  return (int)cudaMemcpyToSymbol(g_bounds_status, zero, sizeof(zero));
+}
+#endif
 
 // ---- pointwise family -------------------------------------------------------------------
 // CTAs of `kern` that fit on the device at once.  Persistent kernels launch exactly this
@@ -246,11 +276,81 @@ template <class Body> int launch_pointwise(const Body& body, long long xnumel, v
 // thread to column vec_col(i) + j of the row, exactly as RowCtx does for the prebuilt bodies.
 // FULL: the row fills every vector of the team exactly (length == TEAM * VPT * kVec), so no
 // element needs a validity test.
+//
+// A generated row body has four parts:
+//   Consts / init(c, k)            operands that do not change from row to row (per-column
+//                                  scales and shifts): loaded and widened once per thread
+//   Raw / fetch(c, x, raw)         the 128-bit vectors of the operands streamed once per row,
+//                                  requested one row ahead of the arithmetic
+//   row<STAGED>(c, k, x, raw)      the math of row x; STAGED says whether `raw` was fetched
+//                                  (aligned operands) or the body loads for itself
+//   prefetch(c, x)                 L2 prefetch of the streamed operands of a later row
+
+// raw 128-bit vectors of one row-shaped operand of storage type U, as one thread holds them
+template <class U, int VPT, int KVEC> struct RawRow {
+  static constexpr int kChunks = KVEC * (int)sizeof(U) / 16;  // 128-bit words per vector
+  static_assert(kChunks >= 1, "staged operands are at least as wide as the row's vector type");
+  uint4 q[VPT][kChunks];
+};
+
+// exact 64-bit integer reduction operators
+struct ISum {
+  static __device__ __forceinline__ long long id() { return 0; }
+  static __device__ __forceinline__ long long f(long long a, long long b) { return a + b; }
+};
+struct IProd {
+  static __device__ __forceinline__ long long id() { return 1; }
+  static __device__ __forceinline__ long long f(long long a, long long b) { return a * b; }
+};
+struct IMax {
+  static __device__ __forceinline__ long long id() { return (long long)0x8000000000000000ull; }
+  static __device__ __forceinline__ long long f(long long a, long long b) { return a > b ? a : b; }
+};
+struct IMin {
+  static __device__ __forceinline__ long long id() { return 0x7fffffffffffffffLL; }
+  static __device__ __forceinline__ long long f(long long a, long long b) { return a < b ? a : b; }
+};
+
+// references to up to two float vectors (operands of the online-softmax riders)
+template <int E, int K> struct VecRefs {
+  const vf<E>* p[K > 0 ? K : 1];
+};
+template <int E> __device__ __forceinline__ VecRefs<E, 0> refs() { return VecRefs<E, 0>{{nullptr}}; }
+template <int E> __device__ __forceinline__ VecRefs<E, 1> refs(const vf<E>& a) { return VecRefs<E, 1>{{&a}}; }
+template <int E> __device__ __forceinline__ VecRefs<E, 2> refs(const vf<E>& a, const vf<E>& b) {
+  return VecRefs<E, 2>{{&a, &b}};
+}
+
+// one warp-level sum of K values: every lane receives every total
+template <int K> __device__ __forceinline__ void warp_sum(float (&v)[K]) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] += __shfl_xor_sync(kFull, v[k], o);
+}
+// NaN-propagating maximum / minimum of a warp in one instruction
+__device__ __forceinline__ float warp_max_nan(float v) {
+  float r;
+  asm volatile("redux.sync.max.NaN.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float warp_min_nan(float v) {
+  float r;
+  asm volatile("redux.sync.min.NaN.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+template <class Op> __device__ __forceinline__ float warp_all(float v) {
+  if constexpr (std::is_same<Op, MaxOp>::value) return warp_max_nan(v);
+  else if constexpr (std::is_same<Op, MinOp>::value) return warp_min_nan(v);
+  else return warp_reduce<Op>(v);
+}
+
 template <typename T, int TEAM, int TEAMS, int VPT, bool FULL = false>
 struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   using Base = RowCtx<T, TEAM, TEAMS, VPT, false>;
   static constexpr int kE = VPT * Base::kVec;
   static constexpr int kGroup = TEAM < 32 ? TEAM : 32;  // lanes of one warp that share a row
+  static constexpr int kW = Base::kWarpsPerTeam;        // warps per team (0 for sub-warp teams)
   // Teams narrower than a warp share their warp's control flow: a team whose row index
   // ran past the end repeats the last row with `live` false, which masks its stores.
   bool live = true;
@@ -290,6 +390,35 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     }
     return r;
   }
+  // the same operand as raw 128-bit vectors (aligned rows only; vectors past the end of a
+  // ragged row read as zero): requested a row ahead, widened when the row is worked on
+  template <class U> __device__ __forceinline__ void fetch_row(const U* rowp, RawRow<U, VPT, Base::kVec>& raw) const {
+    constexpr int kC = RawRow<U, VPT, Base::kVec>::kChunks;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c0 = this->vec_col(i);
+#pragma unroll
+      for (int k = 0; k < kC; ++k)
+        raw.q[i][k] = (FULL || c0 < this->cols) ? ldg_stream(reinterpret_cast<const uint4*>(rowp + c0) + k)
+                                               : make_uint4(0, 0, 0, 0);
+    }
+  }
+  template <class U> __device__ __forceinline__ vf<kE> widen(const RawRow<U, VPT, Base::kVec>& raw) const {
+    constexpr int kC = RawRow<U, VPT, Base::kVec>::kChunks;
+    constexpr int kPer = 16 / (int)sizeof(U);
+    vf<kE> r;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int k = 0; k < kC; ++k) unpack<U>(raw.q[i][k], &r.v[i * Base::kVec + k * kPer]);
+    return r;
+  }
+  // a streamed operand inside row(): from the fetched vectors, or loaded on the spot
+  template <bool STAGED, class U>
+  __device__ __forceinline__ vf<kE> operand(const RawRow<U, VPT, Base::kVec>& raw, const U* rowp) const {
+    if constexpr (STAGED) return widen<U>(raw);
+    else return load_row(rowp);
+  }
   // ask L2 for the lines of a row-contiguous operand this thread will load later: the
   // thread whose vector opens a 128-byte line (or the row itself) issues the prefetch
   template <class U> __device__ __forceinline__ void prefetch_row(const U* rowp) const {
@@ -314,17 +443,152 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
       stvec<U, Base::kVec>(rowp + c0, left > 0 ? left : 0, part);
     }
   }
+  // aligned rows: one 128-bit streaming store per vector, no address test
+  template <bool STAGED, class U, class A> __device__ __forceinline__ void put_row(U* rowp, const A& val) const {
+    if constexpr (STAGED && std::is_same<typename Mem<U>::val, float>::value && (sizeof(U) == 2 || sizeof(U) == 4) &&
+                  std::is_same<A, vf<kE>>::value) {
+      if (!live) return;
+      constexpr int kPer = 16 / (int)sizeof(U);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c0 = this->vec_col(i);
+        if (FULL || c0 < this->cols) {
+#pragma unroll
+          for (int k = 0; k < Base::kVec / kPer; ++k)
+            stg_stream(rowp + c0 + k * kPer, pack<U>(&val.v[i * Base::kVec + k * kPer]));
+        }
+      }
+    } else {
+      store_row(rowp, val);
+    }
+  }
+
+  // ---- team exchange --------------------------------------------------------------------
+  // Partial results cross warps through one 16-byte slot per warp; after the team barrier
+  // lane l of every warp reads the slot of warp l mod kW and a shuffle tree over kW lanes
+  // folds them, so the cost per thread does not grow with the number of warps in the team.
+  __device__ __forceinline__ float* slot_base() { return this->red + this->phase * kW * 4; }
+  template <class Op> __device__ __forceinline__ float xreduce(float v) {
+    if constexpr (TEAM < 32) {
+      return lane_group_reduce<Op, TEAM>(v);
+    } else {
+      v = warp_all<Op>(v);
+      if constexpr (kW > 1) {
+        float* slot = slot_base();
+        if ((this->lane & 31) == 0) slot[(this->lane >> 5) * 4] = v;
+        team_barrier(this->team + 1, TEAM);
+        v = slot[(this->lane & (kW - 1)) * 4];
+        v = lane_group_reduce<Op, kW>(v);
+        this->phase ^= 1;
+      }
+      return v;
+    }
+  }
+  // K sums with one barrier (K <= 4)
+  template <int K> __device__ __forceinline__ void xsum(float (&v)[K]) {
+    static_assert(K <= 4, "a slot holds four floats");
+    if constexpr (TEAM < 32) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = lane_group_reduce<SumOp, TEAM>(v[k]);
+    } else {
+      warp_sum<K>(v);
+      if constexpr (kW > 1) {
+        float* slot = slot_base();
+        if ((this->lane & 31) == 0) {
+#pragma unroll
+          for (int k = 0; k < K; ++k) slot[(this->lane >> 5) * 4 + k] = v[k];
+        }
+        team_barrier(this->team + 1, TEAM);
+        const float* mine = slot + (this->lane & (kW - 1)) * 4;
+#pragma unroll
+        for (int k = 0; k < K; ++k) v[k] = lane_group_reduce<SumOp, kW>(mine[k]);
+        this->phase ^= 1;
+      }
+    }
+  }
+
+  // ---- thread-local folds -------------------------------------------------------------------
+  template <class A> __device__ __forceinline__ float local_sum(const A& val) const {
+    if constexpr (FULL && op::is_fvec<A>::value) {
+      float2 acc = op::pr(val, 0);
+#pragma unroll
+      for (int p = 1; p < kE / 2; ++p) acc = add2(acc, op::pr(val, p));
+      return acc.x + acc.y;
+    } else {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int j = 0; j < Base::kVec; ++j)
+          if (inside(i, j)) acc += Cast<float>::from(at(val, i * Base::kVec + j));
+      return acc;
+    }
+  }
+  // sum of a[e] * b[e]
+  template <class A, class B> __device__ __forceinline__ float local_dot(const A& a, const B& b) const {
+    if constexpr (FULL && op::packable2<A, B>::value) {
+      float2 acc = mul2(op::pr(a, 0), op::pr(b, 0));
+#pragma unroll
+      for (int p = 1; p < kE / 2; ++p) acc = fma2(op::pr(a, p), op::pr(b, p), acc);
+      return acc.x + acc.y;
+    } else {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int j = 0; j < Base::kVec; ++j)
+          if (inside(i, j))
+            acc = fmaf(Cast<float>::from(at(a, i * Base::kVec + j)), Cast<float>::from(at(b, i * Base::kVec + j)), acc);
+      return acc;
+    }
+  }
+  template <class Op, class A> __device__ __forceinline__ float local_fold(const A& val) const {
+    if constexpr (std::is_same<Op, SumOp>::value) {
+      return local_sum(val);
+    } else {
+      float acc = Op::identity();
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int j = 0; j < Base::kVec; ++j)
+          if (inside(i, j)) acc = Op::combine(acc, Cast<float>::from(at(val, i * Base::kVec + j)));
+      return acc;
+    }
+  }
+
   // reductions over the valid elements of the row
   template <class Op, class A> __device__ __forceinline__ float reduce(const A& val) {
-    float acc = Op::identity();
+    return xreduce<Op>(local_fold<Op>(val));
+  }
+  // sum of an element-wise product (the multiply rides in the accumulating fma)
+  template <class A, class B> __device__ __forceinline__ float reduce_dot(const A& a, const B& b) {
+    return xreduce<SumOp>(local_dot(a, b));
+  }
+  // Exact integer reductions: 64-bit accumulators, shuffled as two halves, exchanged
+  // through the same slots (a slot holds two 64-bit values).
+  using ISum = ::ixb::gen::ISum;
+  using IProd = ::ixb::gen::IProd;
+  using IMax = ::ixb::gen::IMax;
+  using IMin = ::ixb::gen::IMin;
+  template <class IOp, class A> __device__ __forceinline__ long long reduce_int(const A& val) {
+    long long acc = IOp::id();
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j)
-        if (inside(i, j))
-          acc = Op::combine(acc, Cast<float>::from(at(val, i * Base::kVec + j)));
-    if constexpr (TEAM < 32) return lane_group_reduce<Op, TEAM>(acc);
-    else return Base::template reduce<Op>(acc);
+        if (inside(i, j)) acc = IOp::f(acc, Cast<long long>::from(at(val, i * Base::kVec + j)));
+#pragma unroll
+    for (int o = kGroup / 2; o > 0; o >>= 1) acc = IOp::f(acc, __shfl_xor_sync(kFull, acc, o));
+    if constexpr (kW > 1) {
+      long long* slot = reinterpret_cast<long long*>(slot_base());
+      if ((this->lane & 31) == 0) slot[(this->lane >> 5) * 2] = acc;
+      team_barrier(this->team + 1, TEAM);
+      acc = slot[(this->lane & (kW - 1)) * 2];
+#pragma unroll
+      for (int o = kW / 2; o > 0; o >>= 1) acc = IOp::f(acc, __shfl_xor_sync(kFull, acc, o));
+      this->phase ^= 1;
+    }
+    return acc;
   }
   template <bool IS_MAX, class A> __device__ __forceinline__ long long reduce_arg(const A& val) {
     ArgPair best = ArgOp<IS_MAX>::identity();
@@ -348,31 +612,110 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
       return Base::template reduce_arg<IS_MAX>(best).i;
     }
   }
-  // (row maximum, sum of exp(value - maximum)) with a single exchange: every thread sums
-  // relative to its own maximum and the partial sums are rescaled as they are folded
-  struct MaxSum {
-    float max, sum;
+
+  // ---- online softmax ------------------------------------------------------------------------
+  // One exchange yields the row maximum, the sum of exp(value - maximum) and up to three
+  // further row sums ("riders") that the emitter found it could form before the maximum is
+  // known: NS of them are sums of exp(value - maximum) * w for a vector w (they are
+  // accumulated relative to each thread's own maximum and rescaled as partial results are
+  // folded, like the sum itself), NP are ordinary sums.  The thread keeps its exponentials
+  // relative to its own maximum in `e` and the factor `r` that brings them to the row
+  // maximum, so that exp(value - maximum) costs one multiply afterwards instead of a second
+  // pass over the exponential unit.
+  template <int NS, int NP> struct Online {
+    float max, sum, r;
+    vf<kE> e;
+    float scaled[NS > 0 ? NS : 1], plain[NP > 0 ? NP : 1];
   };
-  template <class A> __device__ __forceinline__ MaxSum online_softmax(const A& val) {
-    constexpr float kLog2e = 1.4426950408889634f;
+  template <int NS, int NP, class A>
+  __device__ __forceinline__ Online<NS, NP> online_softmax(const A& val, const VecRefs<kE, NS>& w,
+                                                            const VecRefs<kE, NP>& pl) {
+    static_assert(NS + NP <= 2, "a slot holds the maximum, the sum and two riders");
+    Online<NS, NP> o;
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
-      for (int j = 0; j < Base::kVec; ++j)
-        if (inside(i, j)) m = fmaxf(m, Cast<float>::from(at(val, i * Base::kVec + j)));
-    if constexpr (TEAM < 32) m = lane_group_reduce<MaxOp, TEAM>(m);  // no exchange to save: plain two-step
-    float s[1] = {0.f}, none[1] = {0.f};
-    const float shift = (m == -INFINITY) ? 0.f : m;
+      for (int j = 0; j < Base::kVec; j += 2) {
+        const int e0 = i * Base::kVec + j;
+        const float a = inside(i, j) ? Cast<float>::from(at(val, e0)) : -INFINITY;
+        const float b = inside(i, j + 1) ? Cast<float>::from(at(val, e0 + 1)) : -INFINITY;
+        m = max3(m, a, b);
+      }
+    // v[0] = sum of exponentials, v[1..NS] scaled riders, then the plain riders
+    float v[1 + NS + NP];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i)
+    for (int k = 0; k < 1 + NS + NP; ++k) v[k] = 0.f;
+    const float shift = (m == -INFINITY) ? 0.f : -m * kLog2e;
+    float2 acc[1 + NS];
 #pragma unroll
-      for (int j = 0; j < Base::kVec; ++j)
-        if (inside(i, j))
-          s[0] += fast_exp2((Cast<float>::from(at(val, i * Base::kVec + j)) - shift) * kLog2e);
-    if constexpr (TEAM < 32) s[0] = lane_group_reduce<SumOp, TEAM>(s[0]);
-    else Base::template reduce_rescaled<1, 0>(m, s, none, kLog2e);
-    return MaxSum{m, s[0]};
+    for (int k = 0; k < 1 + NS; ++k) acc[k] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < kE / 2; ++p) {
+      const float2 x = make_float2(Cast<float>::from(at(val, 2 * p)), Cast<float>::from(at(val, 2 * p + 1)));
+      const float2 t = fma2(x, make_float2(kLog2e, kLog2e), make_float2(shift, shift));
+      float2 ex = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+      if constexpr (!FULL) {
+        if (!inside((2 * p) / Base::kVec, (2 * p) % Base::kVec)) ex.x = 0.f;
+        if (!inside((2 * p + 1) / Base::kVec, (2 * p + 1) % Base::kVec)) ex.y = 0.f;
+      }
+      o.e.v[2 * p] = ex.x;
+      o.e.v[2 * p + 1] = ex.y;
+      acc[0] = add2(acc[0], ex);
+#pragma unroll
+      for (int k = 0; k < NS; ++k) acc[1 + k] = fma2(ex, op::pr(*w.p[k], p), acc[1 + k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 1 + NS; ++k) v[k] = acc[k].x + acc[k].y;
+#pragma unroll
+    for (int k = 0; k < NP; ++k) v[1 + NS + k] = local_sum(*pl.p[k]);
+
+    // warp stage: agree on the warp's maximum, rescale, sum
+    float r;
+    if constexpr (TEAM < 32) {
+      const float mw = lane_group_reduce<FastMaxOp, TEAM>(m);
+      r = (m == -INFINITY) ? 0.f : fast_exp2((m - mw) * kLog2e);
+#pragma unroll
+      for (int k = 0; k < 1 + NS; ++k) v[k] *= r;
+#pragma unroll
+      for (int k = 0; k < 1 + NS + NP; ++k) v[k] = lane_group_reduce<SumOp, TEAM>(v[k]);
+      m = mw;
+    } else {
+      const float mw = warp_max_fast(m);
+      r = (m == -INFINITY) ? 0.f : fast_exp2((m - mw) * kLog2e);
+#pragma unroll
+      for (int k = 0; k < 1 + NS; ++k) v[k] *= r;
+      warp_sum<1 + NS + NP>(v);
+      m = mw;
+      if constexpr (kW > 1) {
+        float* slot = slot_base();
+        if ((this->lane & 31) == 0) {
+          float4 s4 = make_float4(mw, v[0], 0.f, 0.f);
+          if constexpr (1 + NS + NP > 1) s4.z = v[1];
+          if constexpr (1 + NS + NP > 2) s4.w = v[2];
+          *reinterpret_cast<float4*>(slot + (this->lane >> 5) * 4) = s4;
+        }
+        team_barrier(this->team + 1, TEAM);
+        const float4 part = *reinterpret_cast<const float4*>(slot + (this->lane & (kW - 1)) * 4);
+        const float mm = lane_group_reduce<FastMaxOp, kW>(part.x);
+        const float f = (part.x == -INFINITY) ? 0.f : fast_exp2((part.x - mm) * kLog2e);
+        const float pv[3] = {part.y, part.z, part.w};
+#pragma unroll
+        for (int k = 0; k < 1 + NS + NP; ++k)
+          v[k] = lane_group_reduce<SumOp, kW>(k < 1 + NS ? pv[k] * f : pv[k]);
+        r *= (mw == -INFINITY) ? 0.f : fast_exp2((mw - mm) * kLog2e);
+        m = mm;
+        this->phase ^= 1;
+      }
+    }
+    o.max = m;
+    o.sum = v[0];
+    o.r = r;
+#pragma unroll
+    for (int k = 0; k < NS; ++k) o.scaled[k] = v[1 + k];
+#pragma unroll
+    for (int k = 0; k < NP; ++k) o.plain[k] = v[1 + NS + k];
+    return o;
   }
   // (mean, sum of squared deviations, count) of the row with a single exchange: each
   // thread forms the statistics of its own elements and partial statistics are merged
@@ -433,7 +776,22 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   }
 };
 
-template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS, int PF, bool FULL>
+// CTAs of a row kernel that fit on one SM, cached per device (the attribute is a property of
+// the device the calling thread has current; several host threads may ask at once)
+template <class K> inline int row_resident(K kern, int threads) {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slot = dev & 63;
+  int n = cache[slot].load(std::memory_order_acquire);
+  if (n == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, 0) != cudaSuccess || n < 1) n = 1;
+    cache[slot].store(n, std::memory_order_release);
+  }
+  return n;
+}
+
+template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS, int PF, bool FULL, bool STAGED>
 __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
     row_gen_kernel(const Body body, const long long rows, const int cols) {
   using Ctx = GenRowCtx<T, TEAM, TEAMS, VPT, FULL>;
@@ -445,44 +803,64 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   c.cols = cols;
   c.phase = 0;
   c.red = exchange + c.team * kSlots;
+  // the next launch of the stream may place its CTAs as ours retire; no global access
+  // happens before the launch ahead of us has completed
+  pdl_launch_dependents();
+  pdl_wait();
+  typename Body::Consts k;
+  body.init(c, k);
   const long long stride = (long long)gridDim.x * TEAMS;
   if constexpr (TEAM < 32) {
     // the teams of a warp run the same number of rows (full-mask shuffles inside)
+    typename Body::Raw raw;
     for (long long base = (long long)blockIdx.x * TEAMS; base < rows; base += stride) {
       const long long r = base + c.team;
       c.live = r < rows;
-      body.row(c, c.live ? r : rows - 1);
+      const long long rr = c.live ? r : rows - 1;
+      if constexpr (STAGED) body.fetch(c, rr, raw);
+      body.template row<STAGED>(c, k, rr, raw);
     }
     return;
-  }
-  for (long long r = (long long)blockIdx.x * TEAMS + c.team; r < rows; r += stride) {
-    // PF rows ahead of the one being worked on are on their way from DRAM to L2
-    if constexpr (PF > 0) {
-      const long long ahead = r + PF * stride;
-      if (ahead < rows) body.prefetch(c, ahead);
+  } else {
+    long long r = (long long)blockIdx.x * TEAMS + c.team;
+    typename Body::Raw nxt;
+    if constexpr (STAGED) {
+      if (r < rows) body.fetch(c, r, nxt);
     }
-    body.row(c, r);
+    while (r < rows) {
+      const typename Body::Raw cur = nxt;
+      const long long rn = r + stride;
+      if constexpr (STAGED) {
+        if (rn < rows) body.fetch(c, rn, nxt);
+      }
+      // PF rows beyond the fetched one are on their way from DRAM to L2
+      if constexpr (PF > 0) {
+        const long long ahead = r + (PF + (STAGED ? 1 : 0)) * stride;
+        if (ahead < rows) body.prefetch(c, ahead);
+      }
+      body.template row<STAGED>(c, k, r, cur);
+      r = rn;
+    }
   }
 }
 template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS = 1, int PF = 0, bool FULL = false>
-int launch_row_gen(const Body& body, long long rows, int cols, void* stream) {
+int launch_row_gen(const Body& body, long long rows, int cols, void* stream, bool aligned = false) {
   if (rows <= 0) return 0;
   if (FULL && cols != TEAM * VPT * Elem<T>::kVec) return (int)cudaErrorInvalidValue;
-  auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL>;
-  static int resident = 0;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (resident == 0) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, 0) != cudaSuccess || n < 1) n = 1;
-    resident = n;
-  }
   const long long groups = (rows + TEAMS - 1) / TEAMS;
-  long long grid = (long long)sms * resident;
+  if (aligned) {
+    auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL, true>;
+    long long grid = (long long)sms * row_resident(kern, TEAM * TEAMS);
+    if (grid > groups) grid = groups;
+    return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream, body, rows, cols);
+  }
+  auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL, false>;
+  long long grid = (long long)sms * row_resident(kern, TEAM * TEAMS);
   if (grid > groups) grid = groups;
-  kern<<<(unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream>>>(body, rows, cols);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream, body, rows, cols);
 }
 
 // ---- outer reduction family -----------------------------------------------------------------
@@ -508,6 +886,52 @@ template <int V, int TX, int TY> struct OuterCtx {
     vf<N> r;
 #pragma unroll
     for (int i = 0; i < N; ++i) r.v[i] = v;
+    return r;
+  }
+  using ISum = ::ixb::gen::ISum;
+  using IProd = ::ixb::gen::IProd;
+  using IMax = ::ixb::gen::IMax;
+  using IMin = ::ixb::gen::IMin;
+  template <int N> static __device__ __forceinline__ vi<N> splat_int(long long v) {
+    vi<N> r;
+#pragma unroll
+    for (int i = 0; i < N; ++i) r.v[i] = v;
+    return r;
+  }
+  // exact integer fold: the shared scratch is sized for floats, so the 64-bit partials of
+  // the warps cross it in two rounds (low and high halves would not fold; values do)
+  template <class IOp> __device__ __forceinline__ vi<V> combine_int(const vi<V>& acc) {
+    vi<V> r = acc;
+#pragma unroll
+    for (int off = TX; off < 32; off <<= 1)
+#pragma unroll
+      for (int i = 0; i < V; ++i) r.v[i] = IOp::f(r.v[i], __shfl_xor_sync(kFull, r.v[i], off));
+    if constexpr (kWarps > 1) {
+      const int warp = (ty * TX + tx) >> 5;
+      long long* ipart = reinterpret_cast<long long*>(part);
+      // the scratch holds kWarps * TX * V floats = half as many 64-bit values: fold the
+      // vector in two halves
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        constexpr int HV = (V + 1) / 2;
+        if (ty % kRowsPerWarp == 0) {
+#pragma unroll
+          for (int i = 0; i < HV; ++i)
+            if (h * HV + i < V) ipart[(warp * TX + tx) * HV + i] = r.v[h * HV + i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < HV; ++i) {
+          if (h * HV + i < V) {
+            long long a = ipart[tx * HV + i];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) a = IOp::f(a, ipart[(w * TX + tx) * HV + i]);
+            r.v[h * HV + i] = a;
+          }
+        }
+        __syncthreads();
+      }
+    }
     return r;
   }
   // fold the TY partial vectors; every thread row receives the result

@@ -9,13 +9,49 @@ namespace ixb {
 namespace gen {
 namespace op {
 
+// ---- packed fp32 pairs ----------------------------------------------------------------
+// sm_100 issues fma/mul/add on two fp32 lanes per instruction (f32x2).  Whenever an
+// arithmetic op produces a float vector of even length from float vectors and float
+// scalars, it runs pair by pair through those instructions: half the issue slots of the
+// scalar form.  Integer or boolean operands take the element-wise path.
+template <class T> struct is_fvec { static constexpr bool value = false; };
+template <int N> struct is_fvec<vf<N>> { static constexpr bool value = (N % 2) == 0; };
+template <class T> struct is_fany { static constexpr bool value = is_fvec<T>::value || std::is_same<T, float>::value; };
+template <class A, class B> struct packable2 {
+  static constexpr bool value = (is_fvec<A>::value || is_fvec<B>::value) && is_fany<A>::value && is_fany<B>::value;
+};
+template <class A, class B, class C> struct packable3 {
+  static constexpr bool value = (is_fvec<A>::value || is_fvec<B>::value || is_fvec<C>::value) &&
+                                is_fany<A>::value && is_fany<B>::value && is_fany<C>::value;
+};
+template <int N> __device__ __forceinline__ float2 pr(const vf<N>& a, int p) { return make_float2(a.v[2 * p], a.v[2 * p + 1]); }
+__device__ __forceinline__ float2 pr(float a, int) { return make_float2(a, a); }
+template <int N> __device__ __forceinline__ void set_pr(vf<N>& r, int p, float2 d) {
+  r.v[2 * p] = d.x;
+  r.v[2 * p + 1] = d.y;
+}
+
+// a * b + c with a single rounding (what the compiler's contraction of a*b+c gives for
+// scalar code; the emitter contracts explicitly because packed instructions are opaque to it)
+template <class A, class B, class C>
+__device__ __forceinline__ typename fres<rank3<A, B, C>::n>::type fma(const A& a, const B& b, const C& c) {
+  constexpr int N = rank3<A, B, C>::n;
+  if constexpr (packable3<A, B, C>::value) {
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) set_pr(r, p, fma2(pr(a, p), pr(b, p), pr(c, p)));
+    return r;
+  } else {
+    return map3<typename fres<N>::type>([](float x, float y, float z) { return fmaf(x, y, z); }, a, b, c);
+  }
+}
+
 #define IXB_OP_F1(NAME, EXPR)                                                       \
   template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type NAME(const A& a) { \
     return map1<typename fres<rank<A>::n>::type>([](float x) { return (EXPR); }, a);  \
   }
 // exp / sigmoid use the hardware exponential (ex2.approx on a pre-scaled argument), as
 // Inductor's GPU code generation does for these ops
-IXB_OP_F1(exp, __expf(x))
 IXB_OP_F1(exp2, exp2f(x))
 IXB_OP_F1(expm1, expm1f(x))
 IXB_OP_F1(log, logf(x))
@@ -33,7 +69,6 @@ IXB_OP_F1(atan, atanf(x))
 IXB_OP_F1(sinh, sinhf(x))
 IXB_OP_F1(cosh, coshf(x))
 IXB_OP_F1(tanh, tanhf(x))
-IXB_OP_F1(erf, erff(x))
 IXB_OP_F1(erfc, erfcf(x))
 IXB_OP_F1(lgamma, lgammaf(x))
 IXB_OP_F1(floor, floorf(x))
@@ -41,9 +76,112 @@ IXB_OP_F1(ceil, ceilf(x))
 IXB_OP_F1(trunc, truncf(x))
 IXB_OP_F1(round, nearbyintf(x))
 IXB_OP_F1(reciprocal, 1.f / x)
-IXB_OP_F1(sigmoid, __fdividef(1.f, 1.f + __expf(-x)))
 IXB_OP_F1(to_float, x)
 #undef IXB_OP_F1
+
+// exp(x) = 2^(x * log2 e) on the hardware exponential (ex2.approx), as Inductor's GPU code
+// generation does; the pre-scale runs on packed pairs
+template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type exp(const A& a) {
+  if constexpr (is_fvec<A>::value) {
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) {
+      const float2 t = mul2(pr(a, p), make_float2(kLog2e, kLog2e));
+      set_pr(r, p, make_float2(fast_exp2(t.x), fast_exp2(t.y)));
+    }
+    return r;
+  } else {
+    return map1<typename fres<rank<A>::n>::type>([](float x) { return fast_exp2(x * kLog2e); }, a);
+  }
+}
+// exp(a - b) where b does not vary along the vector (a row statistic): the subtraction and
+// the pre-scale are one packed fma, 2^(a * log2 e - b * log2 e).  The product b * log2 e
+// is rounded once more than in exp(a - b); the emitter uses this form for groups stored in
+// 16-bit types only.
+template <class A>
+__device__ __forceinline__ typename fres<rank<A>::n>::type exp_sub(const A& a, float b) {
+  const float nb = -b * kLog2e;
+  if constexpr (is_fvec<A>::value) {
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) {
+      const float2 t = fma2(pr(a, p), make_float2(kLog2e, kLog2e), make_float2(nb, nb));
+      set_pr(r, p, make_float2(fast_exp2(t.x), fast_exp2(t.y)));
+    }
+    return r;
+  } else {
+    return map1<typename fres<rank<A>::n>::type>([nb](float x) { return fast_exp2(fmaf(x, kLog2e, nb)); }, a);
+  }
+}
+template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type sigmoid(const A& a) {
+  if constexpr (is_fvec<A>::value) {
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) {
+      const float2 t = mul2(pr(a, p), make_float2(-kLog2e, -kLog2e));
+      const float2 d = add2(make_float2(fast_exp2(t.x), fast_exp2(t.y)), make_float2(1.f, 1.f));
+      set_pr(r, p, make_float2(__fdividef(1.f, d.x), __fdividef(1.f, d.y)));
+    }
+    return r;
+  } else {
+    return map1<typename fres<rank<A>::n>::type>(
+        [](float x) { return __fdividef(1.f, 1.f + fast_exp2(-x * kLog2e)); }, a);
+  }
+}
+
+// erf on two values at once, branch-free: |x| <= 1 takes x * P(x^2) (degree 5, relative
+// error 4e-8 against the fp64 function), larger arguments take 1 - 2^-Q(|x|) with Q a
+// degree-6 fit of -log2(erfc) on [1, 4] (absolute error 1e-9); beyond 4 the result is +-1.
+// Both branches run on packed pairs and a select picks per element.
+__device__ __forceinline__ float2 erf2(float2 x) {
+  const float2 t = make_float2(fminf(fabsf(x.x), 4.f), fminf(fabsf(x.y), 4.f));
+  const float2 s = mul2(x, x);
+#define IXB_C2(v) make_float2(v, v)
+  float2 p = fma2(IXB_C2(-0.0005631402018480003f), s, IXB_C2(0.004917546175420284f));
+  p = fma2(p, s, IXB_C2(-0.02671130746603012f));
+  p = fma2(p, s, IXB_C2(0.11280179768800735f));
+  p = fma2(p, s, IXB_C2(-0.37612324953079224f));
+  p = fma2(p, s, IXB_C2(1.1283791065216064f));
+  p = mul2(p, x);
+  // coefficients negated: the polynomial yields -Q, the argument of the exponential
+  float2 q = fma2(IXB_C2(0.0002677357697393745f), t, IXB_C2(-0.004241043236106634f));
+  q = fma2(q, t, IXB_C2(0.03145876154303551f));
+  q = fma2(q, t, IXB_C2(-0.14865218102931976f));
+  q = fma2(q, t, IXB_C2(-0.9207642674446106f));
+  q = fma2(q, t, IXB_C2(-1.625975489616394f));
+  q = fma2(q, t, IXB_C2(-0.0005102010909467936f));
+#undef IXB_C2
+  const float bx = copysignf(1.f - fast_exp2(q.x), x.x);
+  const float by = copysignf(1.f - fast_exp2(q.y), x.y);
+  return make_float2(fabsf(x.x) > 1.f ? bx : p.x, fabsf(x.y) > 1.f ? by : p.y);
+}
+template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type erf(const A& a) {
+  if constexpr (is_fvec<A>::value) {
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) set_pr(r, p, erf2(pr(a, p)));
+    return r;
+  } else {
+    return map1<typename fres<rank<A>::n>::type>([](float x) { return erf2(make_float2(x, x)).x; }, a);
+  }
+}
+// exact-erf GELU, 0.5 * v * (1 + erf(v / sqrt 2)), through the fitted form of common.cuh
+// (absolute error 2.8e-7): the emitter prints this when it recognises the decomposed graph
+template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type gelu_erf(const A& a) {
+  if constexpr (is_fvec<A>::value) {
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) set_pr(r, p, gelu_erf_fast2(pr(a, p)));
+    return r;
+  } else {
+    return map1<typename fres<rank<A>::n>::type>([](float x) { return gelu_erf_fast(x); }, a);
+  }
+}
 
 // abs / neg / square / relu / sign keep the operand's kind (int stays int)
 #define IXB_OP_SAME1(NAME, FEXPR, IEXPR)                                                        \
@@ -104,7 +242,14 @@ template <class A> __device__ __forceinline__ typename fres<rank<A>::n>::type ro
 // reciprocal and N multiplies
 template <class A, class B>
 __device__ __forceinline__ typename fres<rank2<A, B>::n>::type truediv(const A& a, const B& b) {
-  if constexpr (rank<B>::n == 0 && rank<A>::n > 0) {
+  if constexpr (rank<B>::n == 0 && is_fvec<A>::value) {
+    const float inv = 1.f / (float)at(b, 0);
+    constexpr int N = rank<A>::n;
+    vf<N> r;
+#pragma unroll
+    for (int p = 0; p < N / 2; ++p) set_pr(r, p, mul2(pr(a, p), make_float2(inv, inv)));
+    return r;
+  } else if constexpr (rank<B>::n == 0 && rank<A>::n > 0) {
     const float inv = 1.f / (float)at(b, 0);
     return map1<typename fres<rank<A>::n>::type>([inv](float x) { return x * inv; }, a);
   } else {
@@ -129,11 +274,31 @@ IXB_OP_F2(hypot, hypotf(x, y))
       return map2<typename arith<A, B>::type>([](float x, float y) { return (float)(FEXPR); }, a, b); \
     }                                                                                          \
   }
-IXB_OP_ARITH2(add, x + y, x + y)
-IXB_OP_ARITH2(sub, x - y, x - y)
-IXB_OP_ARITH2(mul, x * y, x * y)
-IXB_OP_ARITH2(maximum, (x != x ? x : (y != y ? y : fmaxf(x, y))), (x > y ? x : y))
-IXB_OP_ARITH2(minimum, (x != x ? x : (y != y ? y : fminf(x, y))), (x < y ? x : y))
+#define IXB_OP_PACKED2(NAME, PEXPR, FEXPR, IEXPR)                                               \
+  template <class A, class B>                                                                  \
+  __device__ __forceinline__ typename arith<A, B>::type NAME(const A& a, const B& b) {         \
+    if constexpr (packable2<A, B>::value) {                                                    \
+      constexpr int N = rank2<A, B>::n;                                                        \
+      vf<N> r;                                                                                 \
+      _Pragma("unroll") for (int p = 0; p < N / 2; ++p) {                                      \
+        const float2 x = pr(a, p), y = pr(b, p);                                               \
+        set_pr(r, p, (PEXPR));                                                                 \
+      }                                                                                        \
+      return r;                                                                                \
+    } else if constexpr (arith<A, B>::ints) {                                                  \
+      return map2<typename arith<A, B>::type>(                                                 \
+          [](long long x, long long y) { return (long long)(IEXPR); }, a, b);                  \
+    } else {                                                                                   \
+      return map2<typename arith<A, B>::type>([](float x, float y) { return (float)(FEXPR); }, a, b); \
+    }                                                                                          \
+  }
+IXB_OP_PACKED2(add, add2(x, y), x + y, x + y)
+IXB_OP_PACKED2(sub, fma2(y, make_float2(-1.f, -1.f), x), x - y, x - y)
+IXB_OP_PACKED2(mul, mul2(x, y), x * y, x * y)
+#undef IXB_OP_PACKED2
+// NaN-propagating like torch.maximum / torch.minimum: one max.NaN / min.NaN instruction
+IXB_OP_ARITH2(maximum, MaxOp::combine(x, y), (x > y ? x : y))
+IXB_OP_ARITH2(minimum, MinOp::combine(x, y), (x < y ? x : y))
 // python-style floor division and modulo for integers, C-style truncation for truncdiv
 IXB_OP_ARITH2(floordiv, floorf(x / y), ((x / y) - ((x % y != 0) && ((x < 0) != (y < 0)))))
 IXB_OP_ARITH2(truncdiv, truncf(x / y), x / y)

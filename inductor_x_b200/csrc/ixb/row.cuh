@@ -20,6 +20,7 @@
 //                         CTA-wide barrier if it filled the scratch
 //   row(p, ctx, r, raw)   process row r given its raw vectors raw[k][i]
 #pragma once
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -338,27 +339,49 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   }
 }
 
+// Per-device launch state of one kernel instantiation: the dynamic shared-memory opt-in and
+// the occupancy are properties of (kernel, device), and several host threads may launch at
+// once, so the cache is indexed by the current device and guarded by a mutex.
+struct RowLaunchState {
+  std::mutex mu;
+  size_t configured[64] = {};   // largest dynamic shared-memory size opted in, per device
+  size_t sized_for[64] = {};    // shared-memory size the cached occupancy was computed for
+  int resident[64] = {};        // CTAs per SM (0 = not computed yet)
+};
+template <class K>
+inline cudaError_t row_launch_capacity(RowLaunchState& st, K kern, int threads, size_t smem, int* resident) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const int d = dev & 63;
+  std::lock_guard<std::mutex> lock(st.mu);
+  if (smem > st.configured[d]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    st.configured[d] = smem;
+    st.resident[d] = 0;
+  }
+  if (st.resident[d] == 0 || st.sized_for[d] != smem) {
+    int n = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+    if (e != cudaSuccess) return e;
+    if (n < 1) return cudaErrorInvalidConfiguration;
+    st.resident[d] = n;
+    st.sized_for[d] = smem;
+  }
+  *resident = st.resident[d];
+  return cudaSuccess;
+}
+
 template <class Body, int TEAM, int TEAMS, int VPT, int STAGES, int MIN_CTAS>
 cudaError_t launch_row_staged(const typename Body::Params& p, long long rows, int cols,
                               int sm_count, int grid_override, cudaStream_t stream) {
   auto kern = row_staged_kernel<Body, TEAM, TEAMS, VPT, STAGES, MIN_CTAS>;
   const size_t smem = ((Body::smem_bytes(cols, VPT) + 127) & ~(size_t)127) +
                       (size_t)TEAMS * STAGES * Body::kRowInputs * cols * sizeof(typename Body::in_t);
-  static int resident = 0;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-    resident = 0;
-  }
-  if (resident == 0) {
-    int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, smem);
-    if (e != cudaSuccess) return e;
-    if (n < 1) return cudaErrorInvalidConfiguration;
-    resident = n;
-  }
+  static RowLaunchState state;
+  int resident = 0;
+  if (cudaError_t e = row_launch_capacity(state, kern, TEAM * TEAMS, smem, &resident)) return e;
   const long long groups = (rows + TEAMS - 1) / TEAMS;
   long long grid = (long long)sm_count * resident;
   if (grid_override > 0) grid = grid_override;
@@ -374,21 +397,9 @@ cudaError_t launch_row(const typename Body::Params& p, long long rows, int cols,
                        int grid_override, cudaStream_t stream) {
   auto kern = row_kernel<Body, TEAM, TEAMS, VPT, ALIGNED, MIN_CTAS>;
   const size_t smem = Body::smem_bytes(cols, VPT);
-  static int resident = 0;  // CTAs per SM; identical on every B200 of a box
-  static size_t configured = 0, sized_for = (size_t)-1;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
-  if (resident == 0 || sized_for != smem) {
-    int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, TEAM * TEAMS, smem);
-    if (e != cudaSuccess) return e;
-    if (n < 1) return cudaErrorInvalidConfiguration;
-    resident = n;
-    sized_for = smem;
-  }
+  static RowLaunchState state;
+  int resident = 0;
+  if (cudaError_t e = row_launch_capacity(state, kern, TEAM * TEAMS, smem, &resident)) return e;
   const long long groups = (rows + TEAMS - 1) / TEAMS;
   long long grid = (long long)sm_count * resident;
   if (grid_override > 0) grid = grid_override;

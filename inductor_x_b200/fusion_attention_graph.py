@@ -85,10 +85,16 @@ def _from_bnsd(t: torch.Tensor, layout: str) -> torch.Tensor:
 def _run_kernel(q, k, v, scale: float, causal: bool):
     from . import ops
 
+    from . import config
+
     dt = q.dtype
     if dt == torch.float32:
-        # the reference traces its pattern in fp32 only (:174); the tensor-core kernel
-        # takes 16-bit operands, and fp16 keeps three more mantissa bits than bf16
+        # the reference traces its pattern in fp32 only (:174); the tensor-core kernel takes
+        # 16-bit operands.  Narrowing is the caller's decision, never a silent one: fp16
+        # keeps three more mantissa bits than bf16
+        if not config.attention_fp32_as_fp16:
+            raise TypeError("b200_fa: float32 operands would be narrowed to float16 for the tensor-core "
+                            "kernel; set IXB_ATTENTION_FP32_AS_FP16=1 (config.attention_fp32_as_fp16) to allow it")
         q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
     if q.stride(-1) != 1:
         q = q.contiguous()
@@ -297,11 +303,122 @@ def _b200_fusion_attention_graph_replacement_1(query, key, value, inv_scale_fact
         atten_mask=None, scale=inv_scale_factor, keep_prob=1.0 - dropout_p)[0]
 
 
+# The benchmark configuration writes causal attention out literally:
+#   matmul(q, k^T) -> * scale (or / inv_scale) -> masked_fill(~keep, -inf) -> softmax -> matmul(v)
+# with `keep` a lower-triangular boolean matrix built in the graph (torch.ones(S, S).tril()).
+# The reference's pattern file has no masked form (its pattern 1 above is un-masked); these
+# two search functions extend the same registration to it.  `keep` is a pattern input; the
+# extra check then walks the matched node's producers and accepts the rewrite only if they
+# provably form j <= i (what tril decomposes to), so an arbitrary mask is never dropped.
+def _masked(s, keep):
+    # what masked_fill(~keep, -inf) has become by the time the joint-graph patterns run: a
+    # where() against a 0-d full(-inf) (Inductor folds the scalar_tensor of the decomposition)
+    return torch.where(~keep, torch.full((), float("-inf"), dtype=s.dtype, device=s.device), s)
+
+
+def _b200_causal_attention_pattern_mul(query, key, value, keep, scale):
+    s = _masked(torch.matmul(query, key.transpose(-2, -1)) * scale, keep)
+    return torch.matmul(torch.softmax(s, dim=-1), value)
+
+
+def _b200_causal_attention_pattern_div(query, key, value, keep, inv_scale):
+    s = _masked(torch.matmul(query, key.transpose(-2, -1)) / inv_scale, keep)
+    return torch.matmul(torch.softmax(s, dim=-1), value)
+
+
+def _b200_causal_attention_replacement_mul(query, key, value, keep, scale):
+    from torch._dynamo.utils import counters
+
+    counters["inductor"]["fuse_attention"] += 1
+    # the op takes the divisor (the reference's convention); sparse_mode 3 = causal
+    return b200_fusion_attention_graph(query, key, value, query.size(1), "BNSD", None, atten_mask=None,
+                                       scale=1.0 / scale, keep_prob=1.0, sparse_mode=3)[0]
+
+
+def _b200_causal_attention_replacement_div(query, key, value, keep, inv_scale):
+    from torch._dynamo.utils import counters
+
+    counters["inductor"]["fuse_attention"] += 1
+    return b200_fusion_attention_graph(query, key, value, query.size(1), "BNSD", None, atten_mask=None,
+                                       scale=inv_scale, keep_prob=1.0, sparse_mode=3)[0]
+
+
+def _is_all_true(node) -> bool:
+    if not isinstance(node, torch.fx.Node) or node.op != "call_function":
+        return False
+    if node.target in (aten.full.default,) and len(node.args) >= 2:
+        return node.args[1] is True or node.args[1] == 1
+    if node.target in (aten.ones.default, aten.ones_like.default):
+        return True
+    return False
+
+
+def _iota_axis(node):
+    """-1 if ``node`` is arange(n) laid along the last axis ([1, n] / [n]), -2 if along the
+    second-to-last ([n, 1]); None otherwise."""
+    if not isinstance(node, torch.fx.Node) or node.op != "call_function":
+        return None
+    if node.target is aten.unsqueeze.default:
+        src, dim = node.args
+        if isinstance(src, torch.fx.Node) and src.op == "call_function" and src.target is torch.ops.prims.iota.default:
+            kw = src.kwargs
+            if kw.get("start", 0) == 0 and kw.get("step", 1) == 1:
+                return {-2: -1, 0: -1, -1: -2, 1: -2}.get(dim)
+    return None
+
+
+def _is_lower_triangular(node, depth: int = 0) -> bool:
+    """True when ``node`` provably computes keep[i, j] = (j <= i): the decomposition of
+    ``ones(S, S).tril()`` (``le(sub(iota_j, iota_i), 0)``, possibly and-ed with all-true), its
+    mirrored spellings, or an undecomposed ``tril`` of an all-true matrix."""
+    if depth > 6 or not isinstance(node, torch.fx.Node) or node.op != "call_function":
+        return False
+    t, a = node.target, node.args
+    if t is aten.logical_and.default or t is aten.bitwise_and.Tensor:
+        return (_is_all_true(a[0]) and _is_lower_triangular(a[1], depth + 1)) or \
+               (_is_all_true(a[1]) and _is_lower_triangular(a[0], depth + 1))
+    if t is aten.tril.default:
+        return _is_all_true(a[0]) and (len(a) < 2 or a[1] == 0)
+    if t in (aten.le.Scalar, aten.ge.Scalar) and a[1] == 0 and isinstance(a[0], torch.fx.Node) and \
+            a[0].target is aten.sub.Tensor:
+        lhs, rhs = _iota_axis(a[0].args[0]), _iota_axis(a[0].args[1])
+        # le: (j - i) <= 0; ge: (i - j) >= 0
+        return (lhs, rhs) == ((-1, -2) if t is aten.le.Scalar else (-2, -1))
+    if t in (aten.le.Tensor, aten.ge.Tensor):
+        lhs, rhs = _iota_axis(a[0]), _iota_axis(a[1])
+        return (lhs, rhs) == ((-1, -2) if t is aten.le.Tensor else (-2, -1))
+    return False
+
+
+def _causal_extra_check(match) -> bool:
+    if not _pattern_extra_check(match):
+        return False
+    q, k, v, keep = (match.kwargs.get(n) for n in ("query", "key", "value", "keep"))
+    metas = [getattr(n, "meta", {}).get("val") if n is not None else None for n in (q, k, v, keep)]
+    if any(m is None for m in metas):
+        return False
+    qm, km, vm, mm = metas
+    if km.dim() != 4 or vm.dim() != 4 or km.shape != vm.shape or km.shape[:2] != qm.shape[:2] or km.shape[-1] != 128:
+        return False
+    # top-left and bottom-right causal masks coincide only for equal lengths
+    if qm.shape[2] != km.shape[2] or tuple(mm.shape[-2:]) != (qm.shape[2], km.shape[2]) or mm.dtype != torch.bool:
+        return False
+    if any(int(d) != 1 for d in mm.shape[:-2]):
+        return False
+    return _is_lower_triangular(keep)
+
+
 def _pattern_extra_check(match) -> bool:
     """Only shapes the kernel instantiates: head dim 128."""
+    from . import config
+
     q = match.kwargs.get("query")
     meta = getattr(q, "meta", {}).get("val") if q is not None else None
-    return meta is not None and meta.dim() == 4 and meta.shape[-1] == 128
+    if meta is None or meta.dim() != 4 or meta.shape[-1] != 128:
+        return False
+    if meta.dtype == torch.float32:
+        return config.attention_fp32_as_fp16      # never narrowed without the caller's consent
+    return meta.dtype in (torch.float16, torch.bfloat16)
 
 
 def _get_sfdp_patterns():
@@ -328,6 +445,20 @@ def _get_sfdp_patterns():
             "trace_fn": fwd_only, "pass_dicts": patterns, "scalar_workaround": {},
             "extra_check": _pattern_extra_check,
         }
+    # the masked (causal) form, in the dtypes the kernel takes plus float32 (matched only with
+    # the fp16 opt-in): half types trace differently (casts around the softmax)
+    for dtype in [torch.bfloat16, torch.float16, torch.float]:
+        b_inp = functools.partial(torch.empty, (2, 4, 8, 128), device=device, dtype=dtype)
+        keep = functools.partial(torch.ones, (8, 8), device=device, dtype=torch.bool)
+        c = functools.partial(c_inp, dtype=dtype)      # same dtype: no cast node around the scalar
+        for pattern, replacement in ((_b200_causal_attention_pattern_mul, _b200_causal_attention_replacement_mul),
+                                     (_b200_causal_attention_pattern_div, _b200_causal_attention_replacement_div)):
+            yield f"{pattern.__name__}_{dtype}_inference", {
+                "search_fn": pattern, "replace_fn": replacement,
+                "example_inputs": [b_inp(), b_inp(), b_inp(), keep(), c()],
+                "trace_fn": fwd_only, "pass_dicts": patterns, "scalar_workaround": {},
+                "extra_check": _causal_extra_check,
+            }
 
 
 _fx_pass_registered = False
@@ -420,11 +551,26 @@ class B200AttentionPass(CustomGraphModulePass):
             return None
         qv = q.meta.get("val") if hasattr(q, "meta") else None
         kv = k.meta.get("val") if hasattr(k, "meta") else None
-        if qv is None or kv is None or qv.dim() != 4 or qv.shape[-1] != 128:
+        vv = v.meta.get("val") if hasattr(v, "meta") else None
+        if qv is None or kv is None or vv is None or qv.dim() != 4 or qv.shape[-1] != 128:
             return None
         if qv.dtype not in (torch.float16, torch.bfloat16) or qv.device.type != "cuda":
             return None
-        if causal and kv.shape[2] < qv.shape[2]:
+        # the kernel handles equal head counts, head dim 128 on all three operands, one
+        # dtype and ordinary (positive-stride) layouts; anything else stays with the aten kernel
+        for t in (kv, vv):
+            if t.dim() != 4 or t.shape[0] != qv.shape[0] or t.shape[1] != qv.shape[1] or t.shape[-1] != 128:
+                return None
+            if t.dtype != qv.dtype or t.device != qv.device:
+                return None
+        if kv.shape[2] != vv.shape[2]:
+            return None
+        if any(int(st) <= 0 for t in (qv, kv, vv) for st, n in zip(t.stride(), t.shape) if n > 1):
+            return None
+        # is_causal in torch masks from the top-left corner (key j visible iff j <= i); the
+        # kernel's causal mode is aligned to the bottom-right corner (j <= i + Sk - Sq).  The two
+        # agree only for equal lengths, so a causal node with Sk != Sq is left alone.
+        if causal and kv.shape[2] != qv.shape[2]:
             return None
         scale = kw.get("scale")
         if scale is None:
@@ -432,4 +578,22 @@ class B200AttentionPass(CustomGraphModulePass):
         return q, k, v, float(scale), bool(causal)
 
     def uuid(self):
-        return get_hash_for_files((__file__,))
+        # Part of Inductor's FX-graph cache key.  Everything that changes the text this backend
+        # generates for a given graph has to be in it, or a cached wrapper from an earlier
+        # setting would be served: the code generator's sources, the template headers and the
+        # configuration flags.
+        import glob
+        import hashlib
+        import os
+
+        from . import config
+        from .codegen import jit
+
+        here = os.path.dirname(os.path.abspath(__file__))
+        files = tuple(sorted(glob.glob(os.path.join(here, "*.py")) + glob.glob(os.path.join(here, "codegen", "*.py"))))
+        flags = (config.merged_welford, config.merged_online_softmax, config.debug_bounds, config.fp64_as_fp32,
+                 config.attention_fp32_as_fp16)
+        h = hashlib.sha256(get_hash_for_files(files))
+        h.update(jit._template_digest())
+        h.update(repr(flags).encode())
+        return h.digest()

@@ -15,6 +15,12 @@ import torch
 from . import runtime as rt
 
 
+def launch_count() -> int:
+    """Calls made into the kernel library's launching entry points so far (each enqueues one
+    kernel; a split outer reduction two)."""
+    return rt.native_calls
+
+
 def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:

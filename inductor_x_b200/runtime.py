@@ -138,7 +138,13 @@ def declared_symbols():
     return list(_SIGNATURES)
 
 
+#: kernel-launching entry points of the library called successfully by this process
+native_calls = 0
+
+
 def check(fn: str, status: int) -> None:
+    global native_calls
+    native_calls += 1
     if status != IXB_OK:
         lib = load()
         detail = lib.ixb_strerror(status).decode()

@@ -47,6 +47,27 @@ class OuterAxisShard:
         a, b = shard_bounds(full.shape[0], self.world, self.rank)
         return full[a:b]
 
+    def slot(self, full_out: torch.Tensor) -> torch.Tensor:
+        """This rank's rows of a full-size output buffer (the extent must divide evenly)."""
+        chunk = even_shard(full_out.shape[0], self.world)
+        return full_out[self.rank * chunk:(self.rank + 1) * chunk]
+
+    def run_local(self, fn: Callable, local_input: torch.Tensor, full_out: torch.Tensor,
+                  gather: bool = False) -> torch.Tensor:
+        """For a rank that holds only its own chunk of the input: ``fn(local_input, out=slot)``
+        writes straight into this rank's slot of ``full_out``; with ``gather`` the other ranks'
+        slots are then filled in place."""
+        fn(local_input, out=self.slot(full_out))
+        if gather:
+            self.gather(full_out)
+        return full_out
+
+    def gather(self, full_out: torch.Tensor) -> torch.Tensor:
+        """In-place all-gather: every rank's slot of ``full_out`` travels once over NVLink."""
+        if self.world > 1:
+            dist.all_gather_into_tensor(full_out, self.slot(full_out), group=self.group)
+        return full_out
+
     def run(self, fn: Callable, full_input: torch.Tensor, out_shape_per_item: Tuple[int, ...],
             out_dtype: torch.dtype, gather: bool = False) -> torch.Tensor:
         n = full_input.shape[0]

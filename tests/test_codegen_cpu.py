@@ -37,6 +37,11 @@ def dry_backend(tmp_path_factory):
     config.dry_run = False
 
 
+def launch_shape(code):
+    """(team, teams, vpt) a generated row module names as its default launch shape."""
+    return tuple(int(re.search(rf"#define IXB_ROW_{m} (\d+)", code).group(1)) for m in ("TEAM", "TEAMS", "VPT"))
+
+
 def generated(fn, *args):
     from torch._inductor.utils import run_and_get_code
 
@@ -49,19 +54,53 @@ def test_c1_graph_is_one_row_kernel(dry_backend):
     code = generated(lambda x, w, b: F.gelu(x * w + b).sum(-1), torch.randn(64, 1024), torch.randn(1024),
                      torch.randn(1024))
     assert code.count("ixb_load_kernel('''") == 1
-    assert "launch_row_gen<Body, float, 128, 1, 2, IXB_GEN_MIN_CTAS, 0, true>" in code   # 1024 fp32 = 256 vectors
-    assert code.count("c.load_row(") == 3 and "reduce<ixb::SumOp>" in code
-    assert "triton" not in code.split("ixb_load_kernel")[1]
+    assert launch_shape(code) == (128, 1, 2)              # 1024 fp32 = 256 vectors
+    # w and b are the same for every row: loaded once per thread; x is fetched a row ahead
+    assert code.count("k.k0 = c.load_row(") == 1 and code.count("k.k1 = c.load_row(") == 1
+    assert "c.fetch_row(" in code and "c.template operand<STAGED, float>(raw.s0" in code
+    # x * w + b is one fused multiply-add, the decomposed exact GELU one call
+    assert "ixb::gen::op::fma(" in code and "ixb::gen::op::gelu_erf(" in code
+    assert "reduce<ixb::SumOp>" in code
+    assert "triton_" not in code
 
 
 def test_c2_chain_is_one_row_kernel_with_four_reductions(dry_backend):
     fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5)
     code = generated(fn, torch.randn(32, 4096).bfloat16(), *(torch.randn(4096).bfloat16() for _ in range(3)))
     assert code.count("ixb_load_kernel('''") == 1
-    assert "launch_row_gen<Body, ixb::bf16, 256, 1, 2, IXB_GEN_MIN_CTAS, 0, true>" in code   # 4096 bf16 = 512 vectors
-    assert len(re.findall(r"c\.template reduce<", code)) == 4      # max, sum(exp), mean, variance
+    assert launch_shape(code) == (256, 1, 2)              # 4096 bf16 = 512 vectors
+    # two exchanges per row: the online softmax, which also carries sum(e * g) and sum(x) for
+    # the LayerNorm mean, and the centred second moment
+    assert "c.template online_softmax<1, 1>(tmp1, ixb::gen::refs<kN>(k.k0), ixb::gen::refs<kN>(tmp0))" in code
+    assert ".scaled[0]" in code and ".plain[0]" in code
+    assert len(re.findall(r"c\.template reduce<", code)) == 0 and code.count("c.reduce_dot(") == 1
+    # exp(x - max) / sum comes from the exponentials the exchange kept
+    assert re.search(r"op::mul\(tmp\d+\.e, ixb::gen::op::truediv\(tmp\d+\.r, tmp\d+\)\)", code)
     assert "c.prefetch_row(" in code
-    assert "c.store_row(" in code
+    assert "c.template put_row<STAGED>(" in code
+    assert "tune=dict(" in code and "idempotent=True" in code
+
+
+def test_c2_chain_with_two_pass_softmax(dry_backend):
+    """The same chain with the merged exchange switched off: four plain reductions."""
+    from inductor_x_b200 import config
+
+    fn = lambda x, g, ga, be: F.layer_norm(torch.softmax(x, -1) * g + x, (4096,), ga, be, 1e-5)
+    config.merged_online_softmax = False
+    try:
+        code = generated(fn, torch.randn(32, 4096).bfloat16(), *(torch.randn(4096).bfloat16() for _ in range(3)))
+    finally:
+        config.merged_online_softmax = True
+    assert len(re.findall(r"c\.template reduce<", code)) + code.count("c.reduce_dot(") == 4
+    assert "exp_sub(" in code          # exp(x - rowmax) as one packed fma and the exponential
+
+
+def test_integer_reductions_are_exact_by_construction(dry_backend):
+    code = generated(lambda t: (t.sum(-1), t.amax(-1)), torch.randint(0, 1 << 40, (16, 1000)))
+    assert "reduce_int<typename Ctx::ISum>" in code and "reduce_int<typename Ctx::IMax>" in code
+    assert "to_int(c.template reduce<" not in code
+    code = generated(lambda t: t.sum(0), torch.randint(0, 1 << 40, (256, 1024)))
+    assert "combine_int<typename Ctx::ISum>" in code and "splat_int<kVec>" in code
 
 
 def test_pointwise_uses_128bit_access_when_contiguous(dry_backend):
@@ -92,6 +131,23 @@ def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backen
     # an inner-axis reduction of the same tensor keeps the row mapping
     code = generated(lambda t: t.amax(-1), x)
     assert "launch_row_gen<" in code and "launch_outer_gen" not in code
+
+
+def test_index_analysis_is_structural():
+    """Which addresses a kernel reads is decided from the form of the index, not from
+    sample points: mixed-radix digits of the reduced index must tile its range."""
+    from inductor_x_b200.codegen import ir
+    from torch.utils._sympy.functions import FloorDiv, ModularIndexing
+
+    x, r = sympy.Symbol("xindex", integer=True, nonnegative=True), sympy.Symbol("r0_index", integer=True, nonnegative=True)
+    assert ir.reduction_stride(ModularIndexing(r, 1, 8) + 8 * FloorDiv(r, 8), x, r, 4, 64) == 1
+    assert ir.reduction_stride(ModularIndexing(r, 1, 8) + 8 * ModularIndexing(r, 8, 8) + 64 * x, x, r, 4, 64) == 1
+    assert ir.reduction_stride(ModularIndexing(r, 1, 8) + 8 * ModularIndexing(r, 8, 4) + 64 * x, x, r, 4, 64) is None
+    assert ir.reduction_stride(2 * ModularIndexing(r, 1, 8) + 16 * ModularIndexing(r, 8, 8) + x, x, r, 4, 64) == 2
+    assert ir.reduction_stride(ModularIndexing(x + r, 1, 8), x, r, 4, 64) is None
+    assert ir.row_starts_aligned(r + 4096 * x, x, r, 8) and not ir.row_starts_aligned(r + 1023 * x, x, r, 8)
+    assert ir.x_contiguous_for_all_r(ModularIndexing(x, 1, 64) + 64 * r + 16384 * FloorDiv(x, 64), x, r, 8)
+    assert not ir.x_contiguous_for_all_r(64 * ModularIndexing(x, 1, 64) + r, x, r, 8)
 
 
 def test_index_analysis():

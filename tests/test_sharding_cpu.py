@@ -49,6 +49,13 @@ def _worker(rank, world, port, ret):
         assert torch.allclose(local, torch.nn.functional.gelu(x[a:b]).sum(-1))
         full = sh.run(rowsum, x, (), torch.float32, gather=True)
         assert torch.allclose(full, torch.nn.functional.gelu(x).sum(-1))
+        # a rank that holds only its own chunk writes into its slot of the full buffer and
+        # the gather fills the rest in place
+        buf = torch.full((64,), float("nan"))
+        sh.run_local(rowsum, x[a:b].clone(), buf, gather=False)
+        assert torch.allclose(buf[a:b], torch.nn.functional.gelu(x[a:b]).sum(-1)) and bool(buf.isnan().any())
+        sh.gather(buf)
+        assert torch.allclose(buf, torch.nn.functional.gelu(x).sum(-1))
         ret[rank] = 1
     finally:
         dist.destroy_process_group()
