@@ -121,7 +121,8 @@ class Workload:
         if path == "compiled":
             import inductor_x_b200  # noqa: F401  (registers the backend for "cuda")
 
-            self.compiled = torch.compile(self.graph())
+            # static shapes: a new extent (the row chunks of the end-to-end pipeline) compiles its own module
+            self.compiled = torch.compile(self.graph(), dynamic=False)
         return self
 
     def op(self, *tensors):
@@ -185,7 +186,7 @@ class SoftmaxLayerNorm(Workload):
             return ops.softmax_layernorm(x, *self.params, 1e-5, out=out)
         if not hasattr(self, "compiled_into"):
             fn = self.graph()
-            self.compiled_into = torch.compile(lambda x, g, ga, be, out: out.copy_(fn(x, g, ga, be)))
+            self.compiled_into = torch.compile(lambda x, g, ga, be, out: out.copy_(fn(x, g, ga, be)), dynamic=False)
         return self.compiled_into(x, *self.params, out)
 
     def e2e_setup(self, device, chunks=8):
@@ -797,13 +798,22 @@ def roofline_of(env: Env, wl: Workload, timing: dict):
     ms = timing["kernel_ms_median"]
     work = wl.flops() / 1e3 if tensor else wl.algorithmic_bytes()
     achieved = work / (ms * 1e-3) / 1e9
-    peak = env.peaks["bf16_tflops"] if tensor else env.peaks["hbm_gbs"]
+    # The tensor peak is the cuBLAS figure measured the same way the kernel is: back to back for
+    # a quarter of a second or more the part sits at its power cap and the sustained figure
+    # applies; a shorter region is compared with the burst figure.
+    region_s = timing["kernel_ms_avg"] * timing["steps"] * timing["replays"] * 1e-3
+    sustained = tensor and region_s >= 0.25
+    peak = (env.peaks["bf16_tflops_sustained"] if sustained else env.peaks["bf16_tflops"]) if tensor \
+        else env.peaks["hbm_gbs"]
     traffic = env.traffic.get(f"{wl.name}:{wl.path}", env.traffic.get(wl.name) if wl.path == "prebuilt" else None)
     out = {"bound": "tensor" if tensor else "hbm", "achieved": achieved, "peak": peak,
            "unit": "TFLOP/s" if tensor else "GB/s", "frac": achieved / peak, "traffic": traffic,
            "peak_source": env.peaks["source"], "kernel_ms_avg": timing["kernel_ms_avg"],
            "kernel_ms_median": ms, "kernel_ms_min": timing["kernel_ms_min"],
            "frac_of_nominal": achieved / (2250.0 if tensor else 8000.0)}
+    if tensor:
+        out["peak_kind"] = "sustained" if sustained else "burst"
+        out["frac_of_burst"] = achieved / env.peaks["bf16_tflops"]
     if traffic and not tensor:
         # bytes that actually crossed the DRAM interface (one ncu capture) over the same time: shows
         # how much of `frac` the L2 contributed

@@ -77,8 +77,10 @@ class GeneratedKernel:
         rc = self.fn(pa, ia, stream)
         self.launches += 1
         if rc != 0:
+            hint = (" (a run-time reduced extent beyond the capacity the module was compiled for?)"
+                    if rc == 1 and self.meta.get("family") == "row" else "")
             raise RuntimeError(f"generated kernel {self.meta.get('name', self.key)} failed to launch: "
-                               f"cudaError {rc}")
+                               f"cudaError {rc}{hint}")
         if self.meta.get("bounds"):
             self._raise_on_bad_index()
 
@@ -214,13 +216,13 @@ def source_key(src: str) -> str:
     return hashlib.sha256(_template_digest() + src.encode()).hexdigest()[:24]
 
 
-SHAPE_MACROS = ("IXB_ROW_TEAM", "IXB_ROW_TEAMS", "IXB_ROW_VPT", "IXB_GEN_MIN_CTAS", "IXB_ROW_PF")
+SHAPE_MACROS = ("IXB_ROW_TEAM", "IXB_ROW_TEAMS", "IXB_ROW_VPT", "IXB_GEN_MIN_CTAS", "IXB_ROW_PF", "IXB_ROW_KREGS")
 
 
 def compile_source(src: str, verbose: bool = False, shape=None) -> str:
     """Compile ``src`` into the cache directory (if not already there); returns the .so path.
-    ``shape`` = (team, teams, vpt, min_ctas, prefetch) builds a row module in another launch
-    shape than the one its source names."""
+    ``shape`` = (team, teams, vpt, min_ctas, prefetch, register-resident operands) builds a row
+    module in another launch shape than the one its source names."""
     key = source_key(src)
     os.makedirs(config.cache_dir, exist_ok=True)
     suffix = "" if shape is None else "_" + "x".join(str(int(v)) for v in shape)
@@ -241,8 +243,9 @@ def compile_source(src: str, verbose: bool = False, shape=None) -> str:
     m = re.search(r"#define IXB_GEN_MIN_CTAS (\d+)", src)
     n = int(m.group(1)) if m else None
     if shape is not None:
-        team, teams, vpt, n, pf = (int(v) for v in shape)
-        defines = [f"-DIXB_ROW_TEAM={team}", f"-DIXB_ROW_TEAMS={teams}", f"-DIXB_ROW_VPT={vpt}", f"-DIXB_ROW_PF={pf}"]
+        team, teams, vpt, n, pf, kregs = (int(v) for v in shape)
+        defines = [f"-DIXB_ROW_TEAM={team}", f"-DIXB_ROW_TEAMS={teams}", f"-DIXB_ROW_VPT={vpt}", f"-DIXB_ROW_PF={pf}",
+                   f"-DIXB_ROW_KREGS={kregs}"]
     bounds = [None]
     if n is not None:
         bounds = [n] + [b for b in (6, 4, 3, 2, 1) if b < n]

@@ -49,8 +49,11 @@ REDUCTION_OPS = {
 
 INT_REDUCTION_OPS = {"sum": "ISum", "prod": "IProd", "max": "IMax", "min": "IMin"}
 
-#: registers a thread may spend on operands that are the same for every row
+#: registers a thread may spend on operands that are the same for every row; operands beyond
+#: that budget (the least used ones) live in a shared-memory table
 MAX_CONST_REGS = 64
+#: per-column operands hoisted out of the row loop at most (registers + shared memory)
+MAX_CONSTS = 6
 #: streamed operands fetched one row ahead as raw 128-bit vectors
 MAX_STAGED = 2
 
@@ -92,12 +95,26 @@ class B200Kernel(SIMDKernel):
         self.checked_indices = 0     # data-dependent indices checked on the device (debug builds)
         self.x_indexing = IndentedBuffer()
         self.r_indexing = IndentedBuffer()
+        self.looped = False                      # rows walked in chunks (decided before the range trees exist)
+        self.post_loop_combine = IndentedBuffer()
+        self.post_loop_store = IndentedBuffer()
+        self.outside_loop_vars: set = set()
+        self.n_acc = 0
         super().__init__(tiling, **kwargs)
         self.is_row = self.features.is_reduction()
         if self.is_row:
-            rnumel = self._static_numel("r0_")
+            # a symbolic reduced extent is served up to the capacity of the launch shape chosen
+            # for the extent seen at trace time (the launcher refuses longer rows)
+            rnumel = self._numel_hint("r0_")
             dt = self._narrowest_node_dtype()
-            self._row_cfg = split_tiling.choose_row_config(rnumel, dt, rows=self._static_numel("x"))
+            if self.looped:
+                self._row_cfg = split_tiling.choose_loop_config(dt)
+            else:
+                self._row_cfg = split_tiling.choose_row_config(rnumel, dt, rows=self._numel_hint("x"))
+                if self._row_cfg is None and self._reads_are_strided():
+                    # an outer reduction of any length: the outer mapping loops over the reduced
+                    # axis itself; the row text is never used
+                    self._row_cfg = split_tiling.choose_loop_config(dt)
             if self._row_cfg is None:
                 raise UnsupportedByTemplates(
                     f"reduced extent {rnumel} does not fit the persistent row template")
@@ -168,7 +185,45 @@ class B200Kernel(SIMDKernel):
 
     # ------------------------------------------------------------------ policy hooks
     def should_use_persistent_reduction(self) -> bool:
-        return True  # the row is always held on chip; oversize rows are rejected above
+        """The row is held on chip by one team when it fits comfortably (up to
+        ``split_tiling.MAX_PERSISTENT_VPT`` vectors per thread at the widest team); a longer
+        stride-1 row is walked in chunks - one loop per reduction, the reference's looped inner
+        reduction (``inductor_x/codegen/triton.py:1208-1253``).  Outer (strided) reductions
+        always use the outer mapping, whose body loops over the reduced axis anyway."""
+        if not self.features.is_reduction():
+            return True
+        try:
+            rnumel = int(self.features.reduction_numel)
+        except TypeError:
+            return True                  # run-time extent: persistent up to the compiled capacity
+        vec = min(max(ixb_config.get_aligned_numel(self._narrowest_node_dtype()), 1), 8)
+        nvec = -(-rnumel // vec)
+        self.looped = nvec > split_tiling.MAX_TEAM * split_tiling.MAX_PERSISTENT_VPT and not self._reads_are_strided()
+        return not self.looped
+
+    def _reads_are_strided(self) -> bool:
+        """True when no read of a reduction node walks a reduced variable with stride 1: an
+        outer reduction (decided from the scheduler nodes, before any code is emitted)."""
+        from torch._inductor.dependencies import MemoryDep
+
+        saw = False
+        for node in self.features.scheduler_nodes():
+            if not node.is_reduction():
+                continue
+            body = getattr(node, "_body", None)
+            reduce_vars = set(getattr(body, "reduce_vars", ()) or ())
+            for dep in node.read_writes.reads:
+                if not isinstance(dep, MemoryDep):
+                    continue
+                rvars = [v for v in dep.var_names if v in reduce_vars] if reduce_vars else list(dep.var_names[-1:])
+                rvars = [v for v in rvars if v in dep.index.free_symbols]
+                if not rvars:
+                    continue
+                saw = True
+                strides = V.graph.sizevars.stride_vars(dep.index, rvars)
+                if any(st == 1 for st in strides):
+                    return False
+        return saw
 
     def should_use_cooperative_reduction(self) -> bool:
         return False
@@ -189,6 +244,19 @@ class B200Kernel(SIMDKernel):
             return int(n)
         except TypeError as e:
             raise UnsupportedByTemplates(f"dynamic extent {n} for '{prefix}'") from e
+
+    def _numel_hint(self, prefix: str) -> int:
+        """The extent if it is static, else the value it had when the graph was traced.  The
+        kept extent may be symbolic (the launcher receives it at run time); the hint only
+        steers choices - launch shape, whether a kernel is worth tuning - never addresses."""
+        n = self.numels.get(prefix, sympy.S.One)
+        try:
+            return int(n)
+        except TypeError:
+            return max(int(V.graph.sizevars.size_hint(n)), 1)
+
+    def _is_dynamic(self, prefix: str = "x") -> bool:
+        return not self.numels.get(prefix, sympy.S.One).is_Integer
 
     def _node_dtypes(self):
         out = []
@@ -263,10 +331,10 @@ class B200Kernel(SIMDKernel):
         """x-vector contiguity of an access for every value of the reduced index, decided
         from the structure of the index (no term may mix the kept and the reduced index)."""
         xr, rr = self._xr_roots()
-        if self._static_numel("x") < self._outer_vec:
+        if self._numel_hint("x") < self._outer_vec:
             return False
         if rr is None or rr.symbol() not in exp.free_symbols:
-            return index_ir.is_vector_contiguous(exp, xr.symbol(), self._outer_vec, self._static_numel("x"))
+            return index_ir.is_vector_contiguous(exp, xr.symbol(), self._outer_vec, self._numel_hint("x"))
         return index_ir.x_contiguous_for_all_r(exp, xr.symbol(), rr.symbol(), self._outer_vec)
 
     # ------------------------------------------------------------------ loads
@@ -309,7 +377,7 @@ class B200Kernel(SIMDKernel):
                 exp = self._expanded(index)
                 if xsym in exp.free_symbols and index_ir.is_vector_constant(exp, xsym, self.vec):
                     line = f"{G}ld_uniform({var}, {G}lane0({idx}), nvalid > 0, {other})"
-                if index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec, self._static_numel("x")):
+                if index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec, self._numel_hint("x")):
                     al = self._fast_flag(exp, self.vec)
                     line = f"{G}ldvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid)"
             return self.cse.generate(self.compute, line, dtype=val_dtype)
@@ -320,8 +388,8 @@ class B200Kernel(SIMDKernel):
         has_r = rr is not None and rr.symbol() in exp.free_symbols
         stride = None
         if not indirect and has_r and self.inside_reduction:
-            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
-                                               self._static_numel("r0_"))
+            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._numel_hint("x"),
+                                               self._numel_hint("r0_"))
         vector_row = has_r or indirect
         row_text = gather.replace("@M@", "rmask" if vector_row else "true")
         const_member = None
@@ -336,8 +404,9 @@ class B200Kernel(SIMDKernel):
                 # the same for every row (a per-column scale or shift): loaded and widened
                 # once per thread while registers allow
                 const_member = next((m for m, ptr, _ in self.consts if ptr == row_ptr), None)
-                if const_member is None and narrow_ok and (len(self.consts) + 1) * n <= MAX_CONST_REGS:
-                    const_member = f"k.k{len(self.consts)}"
+                if const_member is None and narrow_ok and len(self.consts) < MAX_CONSTS and \
+                        cfg.team >= 32 and cfg.vec % 4 == 0 and not self.looped:
+                    const_member = f"@K{len(self.consts)}@"      # final slot and home decided at print time
                     self.consts.append((const_member, row_ptr, n))
                 if const_member is not None:
                     row_text = const_member
@@ -345,8 +414,8 @@ class B200Kernel(SIMDKernel):
                 if row_ptr not in self._row_prefetch:
                     self._row_prefetch.append(row_ptr)     # streamed once per row: worth prefetching
                 aligned = index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
-                    self._static_numel("r0_") % cfg.vec == 0
-                if narrow_ok and aligned and cfg.team >= 32:
+                    not self._is_dynamic("r0_") and self._numel_hint("r0_") % cfg.vec == 0
+                if narrow_ok and aligned and cfg.team >= 32 and not self.looped:
                     member = next((m for m, _, ptr in self.staged if ptr == row_ptr), None)
                     if member is None and len(self.staged) < MAX_STAGED:
                         member = f"raw.s{len(self.staged)}"
@@ -379,14 +448,28 @@ class B200Kernel(SIMDKernel):
         self._refuse_fp64(name, dtype)
         ctype = self.dtype_to_str(dtype)
         idx = self.index_to_str(index)
-        if mode is not None:
+        if mode not in (None, "atomic_add"):
             raise UnsupportedByTemplates(f"store mode {mode}")
         indirect = self._is_indirect(index)
         exp = self._expanded(index)
+        if mode == "atomic_add":
+            if dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int64, torch.int32):
+                raise UnsupportedByTemplates(f"atomic add into {dtype}")
+            # accumulating scatter: one atomic per element, whatever the mapping
+            if not self.is_row:
+                self.compute.writeline(DeferredLine(name, f"{G}scatter_add({var}, {idx}, xmask, {value});"))
+                return
+            xr, rr = self._xr_roots()
+            has_r = (rr is not None and rr.symbol() in exp.free_symbols) or indirect
+            row_text = f"{G}scatter_add({var}, {idx}, {'rmask' if has_r else 'c.leader()'}, {value});"
+            outer_text = f"{G}scatter_add({var}, {idx}, ixb::gen::op::logical_and(xmask, c.writer()), {value});"
+            tag = self._placeholder("S", None, row_text, outer_text, has_r=has_r, in_reduction=self.inside_reduction)
+            self.compute.writeline(DeferredLine(name, tag))
+            return
         if not self.is_row:
             line = f"{G}scatter({var}, {idx}, xmask, {value});"
             if not indirect and index_ir.is_vector_contiguous(exp, self._root("x").symbol(), self.vec,
-                                                              self._static_numel("x")):
+                                                              self._numel_hint("x")):
                 al = self._fast_flag(exp, self.vec)
                 line = f"{G}stvec<{ctype}, kVec, {al}>(({var}) + {G}lane0({idx}), nvalid, {value});"
             self.compute.writeline(DeferredLine(name, line))
@@ -396,19 +479,20 @@ class B200Kernel(SIMDKernel):
         vector_row = has_r or indirect
         row_text = f"{G}scatter({var}, {idx}, {'rmask' if vector_row else 'c.leader()'}, {value});"
         if not indirect and has_r and self.inside_reduction:
-            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._static_numel("x"),
-                                               self._static_numel("r0_"))
+            stride = index_ir.reduction_stride(exp, xr.symbol(), rr.symbol(), self._numel_hint("x"),
+                                               self._numel_hint("r0_"))
             if stride == 1:
                 row_ptr = f"({var}) + ({G}lane0({idx}) - {G}lane0(r0_index))"
                 row_text = f"c.store_row({row_ptr}, {value});"
                 cfg = self._row_cfg
-                if index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
-                        self._static_numel("r0_") % cfg.vec == 0 and dtype in FLOAT_DTYPES and \
+                if not self.looped and index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
+                        not self._is_dynamic("r0_") and self._numel_hint("r0_") % cfg.vec == 0 and \
+                        dtype in FLOAT_DTYPES and \
                         config_bytes(dtype) >= config_bytes(self._narrowest_node_dtype()):
                     row_text = f"c.template put_row<STAGED>({row_ptr}, {value});"
-        outer_text = f"{G}scatter({var}, {idx}, ixb::gen::op::logical_and(xmask, c.ty == 0), {value});"
+        outer_text = f"{G}scatter({var}, {idx}, ixb::gen::op::logical_and(xmask, c.writer()), {value});"
         if not indirect and not has_r and self._outer_x_contiguous(exp):
-            outer_text = (f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), c.ty == 0 ? nvalid : 0, "
+            outer_text = (f"{G}stvec<{ctype}, kVec>(({var}) + {G}lane0({idx}), c.writer() ? nvalid : 0, "
                           f"{value});")
         tag = self._placeholder("S", None, row_text, outer_text, has_r=has_r,
                                 in_reduction=self.inside_reduction)
@@ -418,10 +502,14 @@ class B200Kernel(SIMDKernel):
     def store_reduction(self, name: str, index: sympy.Expr, value: CSEVariable) -> None:
         prior = self.inside_reduction
         self.inside_reduction = False
+        compute = self.compute
+        if self.looped:
+            self.compute = self.post_loop_store      # after the chunk loop that produced the value
         try:
             self.store(name, index, value)
         finally:
             self.inside_reduction = prior
+            self.compute = compute
 
     # ------------------------------------------------------------------ reductions
     def _reduction_marker(self, tag: str) -> None:
@@ -432,7 +520,9 @@ class B200Kernel(SIMDKernel):
         key = (src_dtype, reduction_type, value)
         if key in self.cse.reduction_cache:
             return self.cse.reduction_cache[key]
-        if reduction_type == "welford_reduce" and not ixb_config.merged_welford:
+        if self.looped:
+            result = self._looped_reduction(src_dtype, reduction_type, value)
+        elif reduction_type == "welford_reduce" and not ixb_config.merged_welford:
             result = self.welford_reduce_fallback(dtype, value)
         elif reduction_type == "online_softmax_reduce" and not (ixb_config.merged_online_softmax
                                                                 and src_dtype in FLOAT_DTYPES):
@@ -498,6 +588,56 @@ class B200Kernel(SIMDKernel):
                 self.scalars.add(r.name)
                 self.dag.setdefault(r.name, ("reduction", (reduction_type, value), {}))
         self.cse.reduction_cache[key] = result
+        return result
+
+    def _looped_reduction(self, src_dtype, reduction_type, value):
+        """One reduction of a row walked in chunks: a per-thread accumulator declared ahead of
+        the loop, folded with the chunk's elements inside it, and one team exchange after it."""
+        n = self.n_acc
+        self.n_acc += 1
+        acc = f"_acc{n}"
+        is_int = src_dtype in INT_DTYPES or src_dtype == torch.bool
+        if reduction_type == "welford_reduce":
+            # running (mean, m2, weight) of the thread, merged chunk by chunk, one exchange at the end
+            self.body.writeline(f"typename Ctx::Welford {acc}{{0.f, 0.f, 0.f}};")
+            self.compute.writeline(f"{acc} = Ctx::merge({acc}, c.local_welford({value}));")
+            w = self.cse.generate(self.post_loop_combine, f"c.xwelford({acc})", dtype=torch.float32)
+            result = tuple(self.cse.generate(self.post_loop_combine, f"{w}.{field}", dtype=torch.float32)
+                           for field in ("mean", "m2", "weight"))
+            self.outside_loop_vars.update([w, *result])
+            return result
+        if reduction_type == "online_softmax_reduce":
+            self.body.writeline(f"typename Ctx::MaxSum {acc}{{-INFINITY, 0.f}};")
+            self.compute.writeline(f"c.online_chunk({acc}, {value});")
+            ms = self.cse.generate(self.post_loop_combine, f"c.online_finish({acc})", dtype=torch.float32)
+            result = tuple(self.cse.generate(self.post_loop_combine, f"{ms}.{field}", dtype=torch.float32)
+                           for field in ("max", "sum"))
+            self.outside_loop_vars.update([ms, *result])
+            return result
+        if reduction_type in ("argmax", "argmin"):
+            is_max = "true" if reduction_type == "argmax" else "false"
+            self.body.writeline(f"ixb::ArgPair {acc} = ixb::ArgOp<{is_max}>::identity();")
+            self.compute.writeline(f"{acc} = ixb::ArgOp<{is_max}>::combine({acc}, c.template local_arg<{is_max}>({value}));")
+            text, out_dtype = f"c.template xreduce_arg<{is_max}>({acc})", torch.int64
+        elif reduction_type == "any":
+            self.body.writeline(f"float {acc} = 0.f;")
+            self.compute.writeline(f"{acc} = fmaxf({acc}, c.template local_fold<ixb::MaxOp>("
+                                   f"ixb::gen::op::where({value}, 1.f, 0.f)));")
+            text, out_dtype = f"(c.template xreduce<ixb::MaxOp>({acc}) != 0.f)", torch.bool
+        elif reduction_type in REDUCTION_OPS and is_int:
+            iop = INT_REDUCTION_OPS[reduction_type]
+            self.body.writeline(f"long long {acc} = Ctx::{iop}::id();")
+            self.compute.writeline(f"{acc} = Ctx::{iop}::f({acc}, c.template local_fold_int<typename Ctx::{iop}>({value}));")
+            text, out_dtype = f"c.template xreduce_int<typename Ctx::{iop}>({acc})", torch.int64
+        elif reduction_type in REDUCTION_OPS:
+            op = REDUCTION_OPS[reduction_type]
+            self.body.writeline(f"float {acc} = {op}::identity();")
+            self.compute.writeline(f"{acc} = {op}::combine({acc}, c.template local_fold<{op}>({value}));")
+            text, out_dtype = f"c.template xreduce<{op}>({acc})", torch.float32
+        else:
+            raise UnsupportedByTemplates(f"reduction type {reduction_type} over a row walked in chunks")
+        result = self.cse.generate(self.post_loop_combine, text, dtype=out_dtype)
+        self.outside_loop_vars.add(result)
         return result
 
     # ---- sums that ride in the online-softmax exchange -----------------------------------
@@ -631,12 +771,36 @@ class B200Kernel(SIMDKernel):
 
     # ------------------------------------------------------------------ assembling
     def codegen_body(self) -> None:
-        self.body.splice(self.loads)
-        self.body.splice(self.compute)
-        self.body.splice(self.stores)
+        if self.looped and self.inside_reduction:
+            if not (self.loads or self.compute or self.stores or self.post_loop_combine or self.post_loop_store):
+                return
+            # one pass over the row in chunks; everything the pass needs is (re)loaded inside
+            self.body.writeline("for (int chunk = 0; chunk < c.nchunks(); ++chunk) {")
+            with self.body.indent():
+                self.body.writeline("c.set_chunk(chunk);")
+                self.body.writeline("const auto r0_index = c.rindex();")
+                self.body.writeline("const auto rmask = c.rmask();")
+                self.body.splice(self.r_indexing.getvalue())
+                self.body.splice(self.loads)
+                self.body.splice(self.compute)
+                self.body.splice(self.stores)
+            self.body.writeline("}")
+            self.body.splice(self.post_loop_combine)
+            self.body.splice(self.post_loop_store)
+            # values from inside the loop are out of scope now: later passes reload
+            self.cse.invalidate(self.outside_loop_vars)
+            self._ph_by_key.clear()
+        else:
+            self.body.splice(self.loads)
+            self.body.splice(self.compute)
+            self.body.splice(self.stores)
+            self.body.splice(self.post_loop_combine)
+            self.body.splice(self.post_loop_store)
         self.loads.clear()
         self.compute.clear()
         self.stores.clear()
+        self.post_loop_combine.clear()
+        self.post_loop_store.clear()
 
     def _kernel_args(self):
         """(c declaration, assignment from the launcher's arrays) per argument, in the
@@ -694,11 +858,33 @@ class B200Kernel(SIMDKernel):
         tx = 32
         while tx > 1:
             span = tx * self._outer_vec
-            if span <= self._static_numel("x") and all(
+            if span <= self._numel_hint("x") and all(
                     index_ir.vector_access(v["exp"], xsym, span)[0] for v in loads):
                 break
             tx //= 2
         return tx
+
+    def _outer_split(self):
+        """(threads along the kept axis, cluster size) of the outer mapping.  With fewer tiles
+        than SMs and a long reduced axis the tile narrows (down to 64-byte runs) and a cluster
+        of up to 8 CTAs shares each tile, combining through distributed shared memory - the
+        reference's outer split (inductor_x/codegen/split_tiling.py:159-165) without the trip
+        through global memory.  Integer reductions and run-time extents keep one CTA per tile."""
+        tx = self._outer_tx()
+        red = next(v for v in self._ph.values() if v["kind"] == "R")
+        if red.get("is_int") or self._is_dynamic("r0_") or self._is_dynamic("x"):
+            return tx, 1
+        x, r, vec = self._numel_hint("x"), self._static_numel("r0_"), self._outer_vec
+        sms = ixb_config.num_sms
+        tiles = lambda t: -(-x // (t * vec))
+        elsize = config_bytes(self._narrowest_node_dtype())
+        while tx > 1 and tx * vec * elsize > 64 and tiles(tx) * 8 < sms:
+            tx //= 2
+        cs = 1
+        ty = 256 // tx
+        while cs < 8 and tiles(tx) * cs * 2 <= 2 * sms and r // (ty * cs * 2) >= 8:
+            cs *= 2
+        return (tx, cs) if cs > 1 else (self._outer_tx(), 1)
 
     def _substitute(self, text: str, outer: bool) -> str:
         for tag, v in self._ph.items():
@@ -712,7 +898,7 @@ class B200Kernel(SIMDKernel):
     def codegen_kernel(self, name: Optional[str] = None) -> str:
         self.codegen_body()
         decls, assigns, _ = self._kernel_args()
-        xnumel = self._static_numel("x")
+        xnumel_hint = self._numel_hint("x")
         body_text = self.body.getvalue()
         x_idx, r_idx = self.x_indexing.getvalue(), self.r_indexing.getvalue()
         outer = self.is_row and self._choose_outer(body_text)
@@ -727,9 +913,10 @@ class B200Kernel(SIMDKernel):
             # same body in other shapes (-D...) and keep the one that measures fastest;
             # IXB_GEN_MIN_CTAS bounds the registers and is relaxed by the loader on spills.
             cfg = self._row_cfg
+            kregs = min(len(self.consts), MAX_CONST_REGS // max(cfg.elems_per_thread, 1))
             for macro, val in (("IXB_GEN_MIN_CTAS", cfg.min_ctas), ("IXB_ROW_TEAM", cfg.team),
                                ("IXB_ROW_TEAMS", cfg.teams), ("IXB_ROW_VPT", cfg.vpt),
-                               ("IXB_ROW_PF", cfg.prefetch)):
+                               ("IXB_ROW_PF", cfg.prefetch), ("IXB_ROW_KREGS", kregs)):
                 src.writeline(f"#ifndef {macro}")
                 src.writeline(f"#define {macro} {val}")
                 src.writeline("#endif")
@@ -739,11 +926,13 @@ class B200Kernel(SIMDKernel):
         with src.indent():
             for d in decls:
                 src.writeline(d)
+            if self.is_row and self._is_dynamic("r0_"):
+                src.writeline("long long r_extent;   // reduced extent, known at run time")
             if outer:
                 red_tag, red = next((t, v) for t, v in self._ph.items() if v["kind"] == "R")
                 marker = red_tag.replace("@R", "@B")
                 head, _, tail = body_text.partition(marker)
-                rnumel = self._static_numel("r0_")
+                rnumel = "r_extent" if self._is_dynamic("r0_") else f"{self._static_numel('r0_')}LL"
                 conv = "to_int" if red.get("is_int") else "to_float"
                 acc_line = {
                     "sum": "acc = ixb::gen::op::add(acc, ixb::gen::op::{c}({v}));",
@@ -764,7 +953,7 @@ class B200Kernel(SIMDKernel):
                     else:
                         src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
                     src.writeline("#pragma unroll 8")  # independent loads of eight steps in flight
-                    src.writeline(f"for (long long r0_index = c.ty; r0_index < {rnumel}LL; r0_index += Ctx::kTY) {{")
+                    src.writeline(f"for (long long r0_index = c.rbegin(); r0_index < {rnumel}; r0_index += c.rstep()) {{")
                     with src.indent():
                         src.splice(r_idx)
                         src.splice(self._substitute(head, True))
@@ -776,11 +965,20 @@ class B200Kernel(SIMDKernel):
                 import re
 
                 cfg = self._row_cfg
+                row_body = re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False))
+                # per-column operands, most used first: the first IXB_ROW_KREGS of them are
+                # registers, the others are read from the shared-memory table
+                order = sorted(range(len(self.consts)), key=lambda j: -row_body.count(self.consts[j][0]))
+                for new, old in enumerate(order):
+                    row_body = row_body.replace(self.consts[old][0], f"{G}kget<{new}, IXB_ROW_KREGS>(c, k.k{new})")
                 src.writeline(f"static constexpr int kN = IXB_ROW_VPT * {cfg.vec};   // elements per thread")
+                src.writeline(f"static constexpr bool kLooped = {'true' if self.looped else 'false'};   // row walked in chunks")
+                src.writeline(f"static constexpr int kConsts = {len(self.consts)};")
+                src.writeline("static constexpr int kSmemConsts = kConsts > IXB_ROW_KREGS ? kConsts - IXB_ROW_KREGS : 0;")
                 src.writeline("struct Consts {")
                 with src.indent():
-                    for member, _, _ in self.consts:
-                        src.writeline(f"{G}vf<kN> {member[2:]};")
+                    for new in range(len(order)):
+                        src.writeline(f"{G}vf<kN> k{new};")
                 src.writeline("};")
                 src.writeline("struct Raw {")
                 with src.indent():
@@ -796,8 +994,8 @@ class B200Kernel(SIMDKernel):
                         src.writeline("const auto r0_index = c.rindex();")
                         src.splice(x_idx)
                         src.splice(r_idx)
-                        for member, ptr, _ in self.consts:
-                            src.writeline(f"{member} = c.load_row({ptr});")
+                        for new, old in enumerate(order):
+                            src.writeline(f"{G}kinit<{new}, IXB_ROW_KREGS>(c, k.k{new}, {self.consts[old][1]});")
                 src.writeline("}")
                 # raw vectors of the streamed operands of one row (requested a row ahead)
                 src.writeline("template <class Ctx>")
@@ -814,11 +1012,14 @@ class B200Kernel(SIMDKernel):
                 src.writeline("__device__ __forceinline__ void row(Ctx& c, const Consts& k, const long long xindex, "
                               "const Raw& raw) const {")
                 with src.indent():
-                    src.writeline("const auto r0_index = c.rindex();")
-                    src.writeline("const auto rmask = c.rmask();")
-                    src.splice(x_idx)
-                    src.splice(r_idx)
-                    src.splice(re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False)))
+                    if self.looped:
+                        src.splice(x_idx)        # the reduced index is defined inside each chunk loop
+                    else:
+                        src.writeline("const auto r0_index = c.rindex();")
+                        src.writeline("const auto rmask = c.rmask();")
+                        src.splice(x_idx)
+                        src.splice(r_idx)
+                    src.splice(row_body)
                 src.writeline("}")
                 # L2 prefetch of the streamed operands of a later row
                 src.writeline("template <class Ctx>")
@@ -848,24 +1049,35 @@ class B200Kernel(SIMDKernel):
             src.writeline("Body b;")
             for a in assigns:
                 src.writeline(a)
+            # the kept extent is always the last integer argument: a literal in the wrapper for a
+            # static graph, an expression over the wrapper's size symbols for a dynamic one
+            n_int = len([a for a in assigns if 'ints[' in a])
+            src.writeline(f"const long long xnumel = ints[{n_int}];")
+            if self.is_row and self._is_dynamic("r0_"):
+                src.writeline(f"const long long r_extent = ints[{n_int + 1}];")
+                src.writeline("b.r_extent = r_extent;")
             if outer:
-                src.writeline(f"return {G}launch_outer_gen<Body, {self._outer_tx()}>(b, {xnumel}LL, stream, "
+                tx, cs = self._outer_split()
+                launch = f"launch_outer_gen<Body, {tx}>" if cs == 1 else f"launch_outer_split_gen<Body, {tx}, {cs}>"
+                src.writeline(f"return {G}{launch}(b, xnumel, stream, "
                               f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
             elif self.is_row:
                 cfg = self._row_cfg
-                rnumel = self._static_numel("r0_")
+                dyn_r = self._is_dynamic("r0_")
+                rnumel = "(int)r_extent" if dyn_r else str(self._static_numel("r0_"))
                 # the type that fixes how many elements one 128-bit vector of the row holds
                 narrow = self._narrowest_node_dtype()
                 rt = {torch.float32: "float", torch.bfloat16: "ixb::bf16", torch.float16: "ixb::f16"}.get(
                     narrow, f"ixb::Lanes<{cfg.vec}>")
                 nptr = len([a for a in assigns if 'ptrs[' in a])
                 # FULL: the row fills every vector of the team, no ragged tail to test for
-                src.writeline(f"constexpr bool kFull = IXB_ROW_TEAM * IXB_ROW_VPT * {cfg.vec} == {rnumel};")
+                full = "false" if dyn_r or self.looped else f"IXB_ROW_TEAM * IXB_ROW_VPT * {cfg.vec} == {rnumel}"
+                src.writeline(f"constexpr bool kFull = {full};")
                 src.writeline(f"return {G}launch_row_gen<Body, {rt}, IXB_ROW_TEAM, IXB_ROW_TEAMS, IXB_ROW_VPT, "
-                              f"IXB_GEN_MIN_CTAS, IXB_ROW_PF, kFull>(b, {xnumel}LL, {rnumel}, stream, "
+                              f"IXB_GEN_MIN_CTAS, IXB_ROW_PF, kFull>(b, xnumel, {rnumel}, stream, "
                               f"{G}pointers_aligned(ptrs, {nptr}));")
             else:
-                src.writeline(f"return {G}launch_pointwise<Body>(b, {xnumel}LL, stream, "
+                src.writeline(f"return {G}launch_pointwise<Body>(b, xnumel, stream, "
                               f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
         src.writeline("}")
         if self.checked_indices:
@@ -875,12 +1087,14 @@ class B200Kernel(SIMDKernel):
         meta = f"family={self.mapping!r}"
         if self.checked_indices:
             meta += ", bounds=True"
-        if self.mapping == "row":
+        if self.mapping == "row" and not self._is_dynamic("r0_") and not self.looped:
             cfg = self._row_cfg
             inplace = bool(self.args.inplace_buffers)
-            shapes = split_tiling.row_candidates(self._static_numel("r0_"), cfg, rows=xnumel)
-            meta += (f", tune=dict(default={(cfg.team, cfg.teams, cfg.vpt, cfg.min_ctas, cfg.prefetch)!r}, "
-                     f"candidates={shapes!r}, rows={xnumel}, row_bytes={self._static_numel('r0_') * config_bytes(self._narrowest_node_dtype())}, "
+            kregs = min(len(self.consts), MAX_CONST_REGS // max(cfg.elems_per_thread, 1))
+            shapes = split_tiling.row_candidates(self._static_numel("r0_"), cfg, rows=xnumel_hint,
+                                                 n_consts=len(self.consts), kregs=kregs)
+            meta += (f", tune=dict(default={(cfg.team, cfg.teams, cfg.vpt, cfg.min_ctas, cfg.prefetch, kregs)!r}, "
+                     f"candidates={shapes!r}, rows={xnumel_hint}, row_bytes={self._static_numel('r0_') * config_bytes(self._narrowest_node_dtype())}, "
                      f"idempotent={not inplace!r})")
         return f"ixb_load_kernel('''\n{text}''', {meta})"
 
@@ -889,6 +1103,15 @@ class B200Kernel(SIMDKernel):
         for v in self.args.sizevars:
             wrapper.ensure_size_computed(v)
         _, call_args, _, _ = self.args.python_argdefs()
+        numel = V.graph.sizevars.simplify(self.numels.get("x", sympy.S.One))
+        for sym in sorted(numel.free_symbols, key=str):
+            wrapper.ensure_size_computed(sym)
+        call_args = [*call_args, self.pexpr(numel)]
+        if self.is_row and self._is_dynamic("r0_"):
+            rn = V.graph.sizevars.simplify(self.numels["r0_"])
+            for sym in sorted(rn.free_symbols, key=str):
+                wrapper.ensure_size_computed(sym)
+            call_args.append(self.pexpr(rn))
         device = V.graph.get_current_device_or_throw()
         if device.type == "cuda":
             stream = wrapper.write_get_raw_stream(device.index, V.graph.name)

@@ -55,6 +55,7 @@ def narrowest_dtype(dtypes: Iterable[torch.dtype]) -> torch.dtype:
 MAX_TEAM = 1024
 MIN_TEAM = 8          # teams narrower than a warp serve rows of a few vectors
 MAX_VPT = 32         # beyond 8 the row no longer fits the register file and spills: slow but correct
+MAX_PERSISTENT_VPT = 8   # static rows longer than MAX_TEAM x this many vectors are walked in chunks
 
 
 def choose_row_config(rnumel: int, dtype: torch.dtype, rows: Optional[int] = None,
@@ -91,34 +92,57 @@ def choose_row_config(rnumel: int, dtype: torch.dtype, rows: Optional[int] = Non
                      prefetch=2 if streamed and row_bytes >= 2048 else 0)
 
 
-def row_candidates(rnumel: int, chosen: RowConfig, rows: Optional[int] = None):
-    """Launch shapes worth measuring for a generated row kernel besides ``chosen``:
-    ``(team, teams, vpt, min_ctas, prefetch)`` tuples.  One, two and four vectors per
-    thread over the matching power-of-two team, CTAs of 128 or 256 threads (or one team),
-    registers bounded for 512, 768 or 1024 resident threads per SM.  Shapes that keep the
-    chosen number of vectors per thread come first; the module loader builds the first few
-    and keeps the one with the highest measured bandwidth (``codegen/jit.py``)."""
+def choose_loop_config(dtype: torch.dtype) -> RowConfig:
+    """Launch shape of a row kernel that walks its rows in chunks: one team of 512 threads
+    per CTA, two vectors per thread and chunk, registers bounded for two resident CTAs."""
+    vec = min(max(config.get_aligned_numel(dtype), 1), 8)
+    return RowConfig(team=512, teams=1, vpt=2, vec=vec, min_ctas=2, prefetch=0)
+
+
+def row_candidates(rnumel: int, chosen: RowConfig, rows: Optional[int] = None, n_consts: int = 0,
+                   kregs: int = 0):
+    """Launch shapes worth measuring for a generated row kernel besides the chosen one:
+    ``(team, teams, vpt, min_ctas, prefetch, kregs)`` tuples.  One, two and four vectors per
+    thread over the matching power-of-two team; one, two or three teams per CTA; registers
+    bounded for 256 to 1024 resident threads per SM; and, where the body has per-column
+    operands, how many of them stay in registers (``kregs``; the rest are read from the
+    shared-memory table, which frees registers for more resident warps).  The module loader
+    builds the first few and keeps the one with the highest measured bandwidth
+    (``codegen/jit.py``)."""
     vec = chosen.vec
     nvec = -(-rnumel // vec)
-    out = []
     if chosen.team < 32:
-        return out                        # rows of a few vectors: the static choice stands
-    for vpt in sorted((1, 2, 4), key=lambda v: (v != chosen.vpt, abs(v - chosen.vpt))):
+        return []                         # rows of a few vectors: the static choice stands
+    default = (chosen.team, chosen.teams, chosen.vpt, chosen.min_ctas, chosen.prefetch, kregs)
+    ranked = []
+    for vpt in (1, 2, 4):
         team = 32
         while team < MAX_TEAM and team * vpt < nvec:
             team *= 2
         if team * vpt < nvec or (vpt > 1 and team * (vpt // 2) >= nvec):
             continue                      # does not cover the row / leaves idle vectors
-        for cta in (128, 256):
-            teams = max(1, cta // team)
+        for teams in sorted({max(1, 128 // team), max(1, 256 // team), max(1, 384 // team)}):
             threads = team * teams
-            for resident in (1024, 512, 768):
-                min_ctas = max(1, resident // threads)
-                shape = (team, teams, vpt, min_ctas, chosen.prefetch)
-                if shape not in out:
-                    out.append(shape)
-    default = (chosen.team, chosen.teams, chosen.vpt, chosen.min_ctas, chosen.prefetch)
-    return [s for s in out if s != default]
+            if threads > 1024:
+                continue
+            for min_ctas in (1, 2, 3, 4):
+                if threads * min_ctas > 1024 or (min_ctas > 1 and threads * min_ctas < 256):
+                    continue
+                for kr in sorted({kregs, min(n_consts, 1), 0}, reverse=True):
+                    if kr > n_consts:
+                        continue
+                    shape = (team, teams, vpt, min_ctas, chosen.prefetch, kr)
+                    if shape == default or shape in [s for _, s in ranked]:
+                        continue
+                    # prior for the order of measurement (from sweeps of the softmax ->
+                    # LayerNorm chain): shapes whose registers fit their bound, thick threads
+                    # first (the team exchange is paid per thread), then more resident warps
+                    regs_const = kr * vpt * vec
+                    fits = regs_const + 3 * vpt * vec + 40 <= 65536 // (threads * min_ctas)
+                    score = (not fits, -vpt, -(threads * min_ctas), -kr)
+                    ranked.append((score, shape))
+    ranked.sort(key=lambda t: t[0])
+    return [s for _, s in ranked]
 
 
 def choose_pointwise_vec(dtypes: Iterable[torch.dtype]) -> int:

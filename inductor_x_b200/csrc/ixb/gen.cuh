@@ -19,6 +19,7 @@
 
 #include "gen_ops.cuh"
 #include "row.cuh"
+#include "tma.cuh"
 
 namespace ixb {
 namespace gen {
@@ -136,6 +137,30 @@ __device__ __forceinline__ void scatter(T* p, const I& idx, const M& mask, const
 #pragma unroll
     for (int i = 0; i < N; ++i)
       if (at(mask, i)) Mem<T>::st(p + at(idx, i), Cast<V>::from(at(val, i)));
+  }
+}
+
+// scatter with accumulation (store mode "atomic_add": index_put(accumulate=True), scatter_add
+// and the outer split of the reference, inductor_x/codegen/triton.py:904-905): one atomic add
+// per valid element, in the storage type of the destination
+__device__ __forceinline__ void atomic_add(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add(f16* p, float v) { atomicAdd(p, __float2half_rn(v)); }
+__device__ __forceinline__ void atomic_add(bf16* p, float v) { atomicAdd(p, __float2bfloat16_rn(v)); }
+__device__ __forceinline__ void atomic_add(double* p, float v) { atomicAdd(p, (double)v); }
+__device__ __forceinline__ void atomic_add(long long* p, long long v) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(p), (unsigned long long)v);
+}
+__device__ __forceinline__ void atomic_add(int* p, long long v) { atomicAdd(p, (int)v); }
+template <class T, class I, class M, class A>
+__device__ __forceinline__ void scatter_add(T* p, const I& idx, const M& mask, const A& val) {
+  using V = typename Mem<T>::val;
+  constexpr int N = rank3<I, M, A>::n;
+  if constexpr (N == 0) {
+    if (at(mask, 0)) atomic_add(p + at(idx, 0), Cast<V>::from(at(val, 0)));
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (at(mask, i)) atomic_add(p + at(idx, i), Cast<V>::from(at(val, i)));
   }
 }
 
@@ -351,9 +376,54 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   static constexpr int kE = VPT * Base::kVec;
   static constexpr int kGroup = TEAM < 32 ? TEAM : 32;  // lanes of one warp that share a row
   static constexpr int kW = Base::kWarpsPerTeam;        // warps per team (0 for sub-warp teams)
+  static constexpr int kChains = (kE / 2) >= 4 ? 4 : ((kE / 2) >= 2 ? 2 : 1);  // accumulator chains
   // Teams narrower than a warp share their warp's control flow: a team whose row index
   // ran past the end repeats the last row with `live` false, which masks its stores.
   bool live = true;
+  // Rows longer than the team holds are walked in chunks of kCap columns (looped reduction):
+  // chunk0 is the first column of the current chunk.  vec_col shadows the base-class version,
+  // so every access below is relative to the chunk.
+  int chunk0 = 0;
+  static constexpr int kCap = TEAM * VPT * Base::kVec;
+  __device__ __forceinline__ int vec_col(int i) const { return chunk0 + (this->lane + i * TEAM) * Base::kVec; }
+  __device__ __forceinline__ int nchunks() const { return (this->cols + kCap - 1) / kCap; }
+  __device__ __forceinline__ void set_chunk(int chunk) { chunk0 = chunk * kCap; }
+  // Per-column operands that are not kept in registers live in a CTA-wide shared-memory
+  // table, widened to fp32 once at start-up.  Slot s is laid out [quad][vector] (a quad = four
+  // floats) so that consecutive lanes read consecutive 16-byte words: no bank conflicts.
+  const float4* ktab = nullptr;
+  static constexpr int kQuads = Base::kVec / 4 > 0 ? Base::kVec / 4 : 1;
+  static constexpr int kTabVecs = TEAM * VPT;   // vectors of one row at full capacity
+
+  template <int SLOT, class U> __device__ __forceinline__ void fill_sconst(const U* rowp) const {
+    static_assert(Base::kVec % 4 == 0, "shared-memory operands need whole quads per vector");
+    float4* tab = const_cast<float4*>(ktab) + SLOT * kQuads * kTabVecs;
+    for (int v = threadIdx.x; v < kTabVecs; v += blockDim.x) {
+      const int c0 = v * Base::kVec;
+      const int left = this->cols - c0;
+      const auto part = ldvec<U, Base::kVec>(rowp + (left > 0 ? c0 : 0), left > 0 ? left : 0);
+#pragma unroll
+      for (int q = 0; q < kQuads; ++q)
+        tab[q * kTabVecs + v] = make_float4(part.v[4 * q], part.v[4 * q + 1], part.v[4 * q + 2], part.v[4 * q + 3]);
+    }
+  }
+  template <int SLOT> __device__ __forceinline__ vf<kE> sconst() const {
+    const float4* tab = ktab + SLOT * kQuads * kTabVecs;
+    vf<kE> r;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = this->lane + i * TEAM;
+#pragma unroll
+      for (int q = 0; q < kQuads; ++q) {
+        const float4 f = tab[q * kTabVecs + v];
+        r.v[i * Base::kVec + 4 * q] = f.x;
+        r.v[i * Base::kVec + 4 * q + 1] = f.y;
+        r.v[i * Base::kVec + 4 * q + 2] = f.z;
+        r.v[i * Base::kVec + 4 * q + 3] = f.w;
+      }
+    }
+    return r;
+  }
 
   __device__ __forceinline__ bool leader() const { return this->lane == 0 && live; }
   // element j of vector i lies inside the row
@@ -510,10 +580,16 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   // ---- thread-local folds -------------------------------------------------------------------
   template <class A> __device__ __forceinline__ float local_sum(const A& val) const {
     if constexpr (FULL && op::is_fvec<A>::value) {
-      float2 acc = op::pr(val, 0);
+      // kChains independent chains of packed adds: a single chain would serialise on the
+      // add latency with only a few warps resident
+      float2 acc[kChains];
 #pragma unroll
-      for (int p = 1; p < kE / 2; ++p) acc = add2(acc, op::pr(val, p));
-      return acc.x + acc.y;
+      for (int c = 0; c < kChains; ++c) acc[c] = op::pr(val, c);
+#pragma unroll
+      for (int p = kChains; p < kE / 2; ++p) acc[p % kChains] = add2(acc[p % kChains], op::pr(val, p));
+#pragma unroll
+      for (int c = 1; c < kChains; ++c) acc[0] = add2(acc[0], acc[c]);
+      return acc[0].x + acc[0].y;
     } else {
       float acc = 0.f;
 #pragma unroll
@@ -527,10 +603,14 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   // sum of a[e] * b[e]
   template <class A, class B> __device__ __forceinline__ float local_dot(const A& a, const B& b) const {
     if constexpr (FULL && op::packable2<A, B>::value) {
-      float2 acc = mul2(op::pr(a, 0), op::pr(b, 0));
+      float2 acc[kChains];
 #pragma unroll
-      for (int p = 1; p < kE / 2; ++p) acc = fma2(op::pr(a, p), op::pr(b, p), acc);
-      return acc.x + acc.y;
+      for (int c = 0; c < kChains; ++c) acc[c] = mul2(op::pr(a, c), op::pr(b, c));
+#pragma unroll
+      for (int p = kChains; p < kE / 2; ++p) acc[p % kChains] = fma2(op::pr(a, p), op::pr(b, p), acc[p % kChains]);
+#pragma unroll
+      for (int c = 1; c < kChains; ++c) acc[0] = add2(acc[0], acc[c]);
+      return acc[0].x + acc[0].y;
     } else {
       float acc = 0.f;
 #pragma unroll
@@ -570,13 +650,16 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
   using IProd = ::ixb::gen::IProd;
   using IMax = ::ixb::gen::IMax;
   using IMin = ::ixb::gen::IMin;
-  template <class IOp, class A> __device__ __forceinline__ long long reduce_int(const A& val) {
+  template <class IOp, class A> __device__ __forceinline__ long long local_fold_int(const A& val) const {
     long long acc = IOp::id();
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j)
         if (inside(i, j)) acc = IOp::f(acc, Cast<long long>::from(at(val, i * Base::kVec + j)));
+    return acc;
+  }
+  template <class IOp> __device__ __forceinline__ long long xreduce_int(long long acc) {
 #pragma unroll
     for (int o = kGroup / 2; o > 0; o >>= 1) acc = IOp::f(acc, __shfl_xor_sync(kFull, acc, o));
     if constexpr (kW > 1) {
@@ -590,7 +673,10 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     }
     return acc;
   }
-  template <bool IS_MAX, class A> __device__ __forceinline__ long long reduce_arg(const A& val) {
+  template <class IOp, class A> __device__ __forceinline__ long long reduce_int(const A& val) {
+    return xreduce_int<IOp>(local_fold_int<IOp>(val));
+  }
+  template <bool IS_MAX, class A> __device__ __forceinline__ ArgPair local_arg(const A& val) const {
     ArgPair best = ArgOp<IS_MAX>::identity();
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
@@ -598,7 +684,10 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
       for (int j = 0; j < Base::kVec; ++j)
         if (inside(i, j))
           best = ArgOp<IS_MAX>::combine(
-              best, ArgPair{Cast<float>::from(at(val, i * Base::kVec + j)), (long long)(this->vec_col(i) + j)});
+              best, ArgPair{Cast<float>::from(at(val, i * Base::kVec + j)), (long long)(vec_col(i) + j)});
+    return best;
+  }
+  template <bool IS_MAX> __device__ __forceinline__ long long xreduce_arg(ArgPair best) {
     if constexpr (TEAM < 32) {
 #pragma unroll
       for (int o = TEAM / 2; o > 0; o >>= 1) {
@@ -611,6 +700,9 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     } else {
       return Base::template reduce_arg<IS_MAX>(best).i;
     }
+  }
+  template <bool IS_MAX, class A> __device__ __forceinline__ long long reduce_arg(const A& val) {
+    return xreduce_arg<IS_MAX>(local_arg<IS_MAX>(val));
   }
 
   // ---- online softmax ------------------------------------------------------------------------
@@ -632,7 +724,9 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
                                                             const VecRefs<kE, NP>& pl) {
     static_assert(NS + NP <= 2, "a slot holds the maximum, the sum and two riders");
     Online<NS, NP> o;
-    float m = -INFINITY;
+    float mc[kChains];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) mc[c] = -INFINITY;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
@@ -640,16 +734,21 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
         const int e0 = i * Base::kVec + j;
         const float a = inside(i, j) ? Cast<float>::from(at(val, e0)) : -INFINITY;
         const float b = inside(i, j + 1) ? Cast<float>::from(at(val, e0 + 1)) : -INFINITY;
-        m = max3(m, a, b);
+        mc[(e0 / 2) % kChains] = max3(mc[(e0 / 2) % kChains], a, b);
       }
+    float m = mc[0];
+#pragma unroll
+    for (int c = 1; c < kChains; ++c) m = fmaxf(m, mc[c]);
     // v[0] = sum of exponentials, v[1..NS] scaled riders, then the plain riders
     float v[1 + NS + NP];
 #pragma unroll
     for (int k = 0; k < 1 + NS + NP; ++k) v[k] = 0.f;
     const float shift = (m == -INFINITY) ? 0.f : -m * kLog2e;
-    float2 acc[1 + NS];
+    float2 acc[1 + NS][kChains];
 #pragma unroll
-    for (int k = 0; k < 1 + NS; ++k) acc[k] = make_float2(0.f, 0.f);
+    for (int k = 0; k < 1 + NS; ++k)
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) acc[k][c] = make_float2(0.f, 0.f);
 #pragma unroll
     for (int p = 0; p < kE / 2; ++p) {
       const float2 x = make_float2(Cast<float>::from(at(val, 2 * p)), Cast<float>::from(at(val, 2 * p + 1)));
@@ -661,12 +760,16 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
       }
       o.e.v[2 * p] = ex.x;
       o.e.v[2 * p + 1] = ex.y;
-      acc[0] = add2(acc[0], ex);
+      acc[0][p % kChains] = add2(acc[0][p % kChains], ex);
 #pragma unroll
-      for (int k = 0; k < NS; ++k) acc[1 + k] = fma2(ex, op::pr(*w.p[k], p), acc[1 + k]);
+      for (int k = 0; k < NS; ++k) acc[1 + k][p % kChains] = fma2(ex, op::pr(*w.p[k], p), acc[1 + k][p % kChains]);
     }
 #pragma unroll
-    for (int k = 0; k < 1 + NS; ++k) v[k] = acc[k].x + acc[k].y;
+    for (int k = 0; k < 1 + NS; ++k) {
+#pragma unroll
+      for (int c = 1; c < kChains; ++c) acc[k][0] = add2(acc[k][0], acc[k][c]);
+      v[k] = acc[k][0].x + acc[k][0].y;
+    }
 #pragma unroll
     for (int k = 0; k < NP; ++k) v[1 + NS + k] = local_sum(*pl.p[k]);
 
@@ -729,7 +832,8 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     const float d = b.mean - a.mean;
     return Welford{fmaf(d, w, a.mean), a.m2 + b.m2 + d * d * a.weight * w, n};
   }
-  template <class A> __device__ __forceinline__ Welford welford(const A& val) {
+  // statistics of this thread's elements (two passes over registers: mean, then deviations)
+  template <class A> __device__ __forceinline__ Welford local_welford(const A& val) const {
     float n = 0.f, sum = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
@@ -748,6 +852,10 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
           const float d = Cast<float>::from(at(val, i * Base::kVec + j)) - w.mean;
           w.m2 = fmaf(d, d, w.m2);
         }
+    return w;
+  }
+  // merge the threads' statistics over the team; every thread gets the row's
+  __device__ __forceinline__ Welford xwelford(Welford w) {
 #pragma unroll
     for (int off = kGroup / 2; off > 0; off >>= 1) {
       Welford o{__shfl_xor_sync(0xffffffffu, w.mean, off), __shfl_xor_sync(0xffffffffu, w.m2, off),
@@ -771,21 +879,73 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     }
     return w;
   }
+  template <class A> __device__ __forceinline__ Welford welford(const A& val) { return xwelford(local_welford(val)); }
+  // Online softmax of a row walked in chunks: the running (maximum, sum of exponentials
+  // relative to it) of this thread absorbs one chunk; the team exchange follows the loop.
+  struct MaxSum {
+    float max, sum;
+  };
+  template <class A> __device__ __forceinline__ void online_chunk(MaxSum& acc, const A& val) const {
+    float m = acc.max;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j)) m = fmaxf(m, Cast<float>::from(at(val, i * Base::kVec + j)));
+    if (m == -INFINITY) return;      // nothing but -inf so far
+    float s = acc.sum * fast_exp2((acc.max - m) * kLog2e);   // exp2(-inf) == 0 covers the first chunk
+    const float shift = -m * kLog2e;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j)) s += fast_exp2(fmaf(Cast<float>::from(at(val, i * Base::kVec + j)), kLog2e, shift));
+    acc.max = m;
+    acc.sum = s;
+  }
+  __device__ __forceinline__ MaxSum online_finish(MaxSum acc) {
+    float m = acc.max, s[1] = {acc.sum}, none[1] = {0.f};
+    if constexpr (TEAM < 32) {
+      const float mw = lane_group_reduce<FastMaxOp, TEAM>(m);
+      const float r = (m == -INFINITY) ? 0.f : fast_exp2((m - mw) * kLog2e);
+      return MaxSum{mw, lane_group_reduce<SumOp, TEAM>(s[0] * r)};
+    } else {
+      Base::template reduce_rescaled<1, 0>(m, s, none, kLog2e);
+      return MaxSum{m, s[0]};
+    }
+  }
   template <class A> __device__ __forceinline__ bool reduce_any(const A& val) {
     return reduce<MaxOp>(op::where(val, 1.f, 0.f)) != 0.f;
   }
 };
 
+// Per-column operand J of a generated body: the first KREGS operands (the most used ones) are
+// registers of the thread, the others are read from the shared-memory table when needed.
+template <int J, int KREGS, class Ctx, class U, int E>
+__device__ __forceinline__ void kinit(Ctx& c, vf<E>& reg, const U* rowp) {
+  if constexpr (J < KREGS) reg = c.load_row(rowp);
+  else c.template fill_sconst<J - KREGS>(rowp);
+}
+template <int J, int KREGS, class Ctx, int E>
+__device__ __forceinline__ vf<E> kget(const Ctx& c, const vf<E>& reg) {
+  if constexpr (J < KREGS) return reg;
+  else return c.template sconst<J - KREGS>();
+}
+
 // CTAs of a row kernel that fit on one SM, cached per device (the attribute is a property of
 // the device the calling thread has current; several host threads may ask at once)
-template <class K> inline int row_resident(K kern, int threads) {
+template <class K> inline int row_resident(K kern, int threads, size_t smem = 0) {
   static std::atomic<int> cache[64];
   int dev = 0;
   cudaGetDevice(&dev);
   const int slot = dev & 63;
   int n = cache[slot].load(std::memory_order_acquire);
   if (n == 0) {
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, 0) != cudaSuccess || n < 1) n = 1;
+    // more than 48 KiB of dynamic shared memory needs the opt-in, once per device
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) return -1;
     cache[slot].store(n, std::memory_order_release);
   }
   return n;
@@ -797,18 +957,21 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   using Ctx = GenRowCtx<T, TEAM, TEAMS, VPT, FULL>;
   constexpr int kSlots = TEAM > 32 ? 2 * (TEAM / 32) * 4 : 1;  // exchange floats per team
   __shared__ __align__(16) float exchange[TEAMS * kSlots];
+  extern __shared__ __align__(16) unsigned char operand_table[];   // Body::kSmemConsts slots
   Ctx c;
   c.lane = threadIdx.x % TEAM;
   c.team = threadIdx.x / TEAM;
   c.cols = cols;
   c.phase = 0;
   c.red = exchange + c.team * kSlots;
+  c.ktab = reinterpret_cast<const float4*>(operand_table);
   // the next launch of the stream may place its CTAs as ours retire; no global access
   // happens before the launch ahead of us has completed
   pdl_launch_dependents();
   pdl_wait();
   typename Body::Consts k;
   body.init(c, k);
+  if constexpr (Body::kSmemConsts > 0) __syncthreads();   // the operand table is complete
   const long long stride = (long long)gridDim.x * TEAMS;
   if constexpr (TEAM < 32) {
     // the teams of a warp run the same number of rows (full-mask shuffles inside)
@@ -847,20 +1010,29 @@ template <class Body, typename T, int TEAM, int TEAMS, int VPT, int MIN_CTAS = 1
 int launch_row_gen(const Body& body, long long rows, int cols, void* stream, bool aligned = false) {
   if (rows <= 0) return 0;
   if (FULL && cols != TEAM * VPT * Elem<T>::kVec) return (int)cudaErrorInvalidValue;
+  // a row longer than the team can hold (a run-time extent beyond the compiled capacity);
+  // looped bodies walk any length in chunks
+  if (cols < 0 || (!Body::kLooped && cols > TEAM * VPT * Elem<T>::kVec)) return (int)cudaErrorInvalidValue;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long groups = (rows + TEAMS - 1) / TEAMS;
+  using Ctx = GenRowCtx<T, TEAM, TEAMS, VPT, FULL>;
+  const size_t smem = (size_t)Body::kSmemConsts * Ctx::kQuads * Ctx::kTabVecs * sizeof(float4);
   if (aligned) {
     auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL, true>;
-    long long grid = (long long)sms * row_resident(kern, TEAM * TEAMS);
+    const int resident = row_resident(kern, TEAM * TEAMS, smem);
+    if (resident < 1) return (int)cudaErrorInvalidConfiguration;
+    long long grid = (long long)sms * resident;
     if (grid > groups) grid = groups;
-    return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream, body, rows, cols);
+    return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, smem, (cudaStream_t)stream, body, rows, cols);
   }
   auto kern = row_gen_kernel<Body, T, TEAM, TEAMS, VPT, MIN_CTAS, PF, FULL, false>;
-  long long grid = (long long)sms * row_resident(kern, TEAM * TEAMS);
+  const int resident = row_resident(kern, TEAM * TEAMS, smem);
+  if (resident < 1) return (int)cudaErrorInvalidConfiguration;
+  long long grid = (long long)sms * resident;
   if (grid > groups) grid = groups;
-  return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, 0, (cudaStream_t)stream, body, rows, cols);
+  return (int)launch_pdl(kern, (unsigned)grid, TEAM * TEAMS, smem, (cudaStream_t)stream, body, rows, cols);
 }
 
 // ---- outer reduction family -----------------------------------------------------------------
@@ -881,6 +1053,10 @@ template <int V, int TX, int TY> struct OuterCtx {
   static_assert(TX <= 32 && 32 % TX == 0 && (TX * TY) % 32 == 0, "thread grid must tile warps");
   int tx, ty;
   float* part;  // [kWarps][TX * V]
+  // the reduced indices this thread row walks, and who stores the result of a tile
+  __device__ __forceinline__ long long rbegin() const { return ty; }
+  __device__ __forceinline__ long long rstep() const { return TY; }
+  __device__ __forceinline__ bool writer() const { return ty == 0; }
 
   template <int N> static __device__ __forceinline__ vf<N> splat(float v) {
     vf<N> r;
@@ -979,6 +1155,131 @@ __global__ void __launch_bounds__(TX* TY) outer_gen_kernel(const Body body, cons
     else body.template tile<false>(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
   }
 }
+// ---- outer reduction split over a thread-block cluster -----------------------------------------
+// When the kept extent gives fewer tiles than the GPU has SMs and the reduced axis is long, a
+// cluster of CS CTAs shares one tile: rank k walks the reduced indices k * TY + ty, + TY * CS, ...
+// and the partial vectors meet in the shared memory of rank 0 (distributed shared memory):
+// every other rank stores its vector there (st.shared::cluster to the address mapa gives) and
+// arrives on rank 0's mbarrier with cluster-scope release; rank 0 waits on it with a bounded
+// acquire wait, folds and stores.  This is the reference's outer split
+// (inductor_x/codegen/split_tiling.py:159-165), which combines with atomic adds in global
+// memory; here nothing leaves the chip.  One tile per cluster, so the inbox is used once.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(const void* local_smem, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+// bounded wait with cluster-scope acquire (the data was written by other CTAs of the cluster)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, 1000000;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicAdd(&g_wait_timeouts, 1u);
+      return false;
+    }
+  }
+}
+
+template <int V, int TX, int TY, int CS> struct OuterSplitCtx : OuterCtx<V, TX, TY> {
+  using Base = OuterCtx<V, TX, TY>;
+  int rank = 0;      // CTA rank inside the cluster
+  float* inbox;      // [CS - 1][TX * V]; only rank 0's copy is written to
+  uint64_t* bar;     // arrivals of the other ranks; only rank 0's copy is used
+  bool ok = true;    // false after rank 0's wait gave up: the tile is not stored
+  __device__ __forceinline__ long long rbegin() const { return (long long)rank * TY + this->ty; }
+  __device__ __forceinline__ long long rstep() const { return (long long)TY * CS; }
+  __device__ __forceinline__ bool writer() const { return this->ty == 0 && rank == 0 && ok; }
+  template <class Op> __device__ __forceinline__ vf<V> combine(const vf<V>& acc) {
+    vf<V> r = Base::template combine<Op>(acc);   // the CTA's own partial, in every thread row
+    if (this->ty != 0) return r;
+    if (rank != 0) {
+      const uint32_t dst = map_to_rank(inbox + ((rank - 1) * TX + this->tx) * V, 0);
+#pragma unroll
+      for (int i = 0; i < V; ++i) st_cluster_f32(dst + 4 * i, r.v[i]);
+      mbar_arrive_remote(map_to_rank(bar, 0));
+    } else {
+      ok = mbar_wait_cluster(bar, 0);
+      if (ok) {
+#pragma unroll
+        for (int k = 0; k < CS - 1; ++k)
+#pragma unroll
+          for (int i = 0; i < V; ++i) r.v[i] = Op::combine(r.v[i], inbox[(k * TX + this->tx) * V + i]);
+      }
+    }
+    return r;
+  }
+};
+
+template <class Body, int TX, int TY, int CS, bool ALIGNED>
+__global__ void __launch_bounds__(TX* TY) outer_split_gen_kernel(const Body body, const long long xnumel) {
+  constexpr int V = Body::kVec;
+  __shared__ __align__(16) float part[(TX * TY / 32) * TX * V];
+  __shared__ __align__(16) float inbox[(CS - 1) * TX * V];
+  __shared__ __align__(8) uint64_t bar;
+  OuterSplitCtx<V, TX, TY, CS> c;
+  c.tx = threadIdx.x % TX;
+  c.ty = threadIdx.x / TX;
+  c.part = part;
+  c.inbox = inbox;
+  c.bar = &bar;
+  c.rank = (int)cluster_rank();
+  if (c.rank == 0 && threadIdx.x == 0) {
+    mbar_init(&bar, (CS - 1) * TX);
+    mbar_init_fence();
+  }
+  // every CTA of the cluster is resident and rank 0's barrier is initialised before anyone pushes
+  cluster_sync_all();
+  const long long per_cta = (long long)TX * V;
+  const long long t = blockIdx.x / CS;   // one tile per cluster
+  const long long xbase = t * per_cta + (long long)c.tx * V;
+  const long long left = xnumel - xbase;
+  if (ALIGNED && xnumel - t * per_cta >= per_cta) body.template tile<true>(c, xbase, V);
+  else body.template tile<false>(c, xbase, left >= V ? V : (left > 0 ? (int)left : 0));
+}
+template <class Body, int TX, int CS>
+int launch_outer_split_gen(const Body& body, long long xnumel, void* stream, bool aligned = false) {
+  if (xnumel <= 0) return 0;
+  constexpr int TY = 256 / TX;
+  const long long per_cta = (long long)TX * Body::kVec;
+  const long long tiles = (xnumel + per_cta - 1) / per_cta;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * CS));
+  cfg.blockDim = dim3(TX * TY);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (aligned) return (int)cudaLaunchKernelEx(&cfg, outer_split_gen_kernel<Body, TX, TY, CS, true>, body, xnumel);
+  return (int)cudaLaunchKernelEx(&cfg, outer_split_gen_kernel<Body, TX, TY, CS, false>, body, xnumel);
+}
+
 template <class Body, int TX = 32>
 int launch_outer_gen(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;

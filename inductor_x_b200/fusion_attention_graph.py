@@ -330,17 +330,16 @@ def _b200_causal_attention_replacement_mul(query, key, value, keep, scale):
     from torch._dynamo.utils import counters
 
     counters["inductor"]["fuse_attention"] += 1
-    # the op takes the divisor (the reference's convention); sparse_mode 3 = causal
-    return b200_fusion_attention_graph(query, key, value, query.size(1), "BNSD", None, atten_mask=None,
-                                       scale=1.0 / scale, keep_prob=1.0, sparse_mode=3)[0]
+    # forward-only graph: the compact op (result and log-sum-exp, no [B, N, S, 8] statistics to
+    # materialise); causal with equal lengths, which the extra check established
+    return torch.ops.b200_graph.b200_sdpa(query, key, value, scale, True)[0]
 
 
 def _b200_causal_attention_replacement_div(query, key, value, keep, inv_scale):
     from torch._dynamo.utils import counters
 
     counters["inductor"]["fuse_attention"] += 1
-    return b200_fusion_attention_graph(query, key, value, query.size(1), "BNSD", None, atten_mask=None,
-                                       scale=inv_scale, keep_prob=1.0, sparse_mode=3)[0]
+    return torch.ops.b200_graph.b200_sdpa(query, key, value, 1.0 / inv_scale, True)[0]
 
 
 def _is_all_true(node) -> bool:
@@ -430,12 +429,14 @@ def _get_sfdp_patterns():
     g_inp = functools.partial(torch.empty, (2, 4, 8, 16), device=device, requires_grad=True)
     c_inp = functools.partial(torch.tensor, 2.0, device=device)
     workaround = {"dropout_p": 0.113377}
-    for dtype in [torch.float]:
+    # the reference traces float32 only; half types trace differently (casts around the
+    # softmax) and are what the kernel takes, so the pattern is registered for them as well
+    for dtype in [torch.float, torch.bfloat16, torch.float16]:
         g = functools.partial(g_inp, dtype=dtype)
         c = functools.partial(c_inp, dtype=dtype)
         pattern, replacement = _b200_fusion_attention_graph_pattern_1, _b200_fusion_attention_graph_replacement_1
         args = [g(), g(), g(), c()]
-        name = pattern.__name__
+        name = f"{pattern.__name__}_{dtype}"
         # the training (joint) variant is registered only when a backward kernel exists;
         # the inference variant drops dropout, exactly as the reference partialises it
         pattern_i = partialize_and_update_signature(pattern, dropout_p=0.0)

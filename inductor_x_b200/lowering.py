@@ -9,8 +9,9 @@ What changed underneath.  The reference whitelists ~50 aten ops (``GENERATE_LIST
 ``:80-148``) and turns *everything else* into an extern call, so e.g. ``gelu``, ``sigmoid``,
 ``pow``, ``sin/cos`` and ``index_select`` break fusion.  Here the templates instantiate any
 pointwise / reduction / indexing body, so the policy is inverted: only the op families no
-template exists for (scans, sorts, random numbers, scatter-with-atomics) are forced to
-extern kernels.  The reference's special lowerings are not carried over where they encode
+template exists for (scans, sorts, random numbers, scatter with a reduction other than add)
+are forced to extern kernels; accumulating scatters (``index_put(accumulate=True)``,
+``scatter_add``, ``index_add``) are generated with atomic adds.  The reference's special lowerings are not carried over where they encode
 bugs or NPU workarounds: ``sum_`` always returning fp32 (``:204-215``), the hard-coded
 ``[32768, 2]`` fallback (``:211-212``), ``embedding`` ignoring ``padding_idx``
 (``:327-330``).  fp32 accumulation for half inputs and the two-pass variance
@@ -30,8 +31,7 @@ prims = torch.ops.prims
 # op families without a B200 template: they stay extern (ATen) kernels
 FALLBACK_LIST = [
     aten.cumsum, aten.cumprod, aten.cummax, aten.cummin, aten.logcumsumexp,
-    aten.sort, aten.topk, aten.scatter_add, aten.scatter_reduce, aten.index_put,
-    aten.index_add, aten.bernoulli, aten.rand, aten.randn, aten.randint, aten.randperm,
+    aten.sort, aten.topk, aten.scatter_reduce, aten.bernoulli, aten.rand, aten.randn, aten.randint, aten.randperm,
     aten.native_dropout, aten.multinomial, aten.bucketize, aten.searchsorted, aten.histc,
 ]
 

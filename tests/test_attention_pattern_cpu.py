@@ -54,7 +54,7 @@ def test_literal_causal_attention_is_matched(dtype, form):
     configuration 4 writes it, becomes one b200_fa call and both batched matmuls disappear."""
     q, k, v = (torch.randn(2, 4, 64, 128).to(dtype) for _ in range(3))
     targets = _targets_after_joint_passes(_literal_attention("tril", form, 1 / math.sqrt(128)), q, k, v)
-    assert "b200_graph.b200_fa.default" in targets
+    assert "b200_graph.b200_sdpa.default" in targets
     assert "aten.bmm.default" not in targets
 
 
@@ -62,7 +62,7 @@ def test_masks_that_are_not_provably_causal_are_left_alone():
     q, k, v = (torch.randn(2, 4, 64, 128).bfloat16() for _ in range(3))
     # upper-triangular mask built in the graph
     targets = _targets_after_joint_passes(_literal_attention("triu", "mul", 0.1), q, k, v)
-    assert "b200_graph.b200_fa.default" not in targets and targets.count("aten.bmm.default") == 2
+    assert "b200_graph.b200_sdpa.default" not in targets and targets.count("aten.bmm.default") == 2
     # a mask that is a graph input: nothing can be proven about it
     keep = torch.ones(64, 64, dtype=torch.bool).tril()
 
@@ -71,7 +71,7 @@ def test_masks_that_are_not_provably_causal_are_left_alone():
         return torch.matmul(torch.softmax(s, dim=-1), v)
 
     targets = _targets_after_joint_passes(with_input_mask, q, k, v, keep)
-    assert "b200_graph.b200_fa.default" not in targets
+    assert "b200_graph.b200_sdpa.default" not in targets
     # longer key sequence: top-left and bottom-right causal masks differ
 
     def longer_keys(q, k, v):
@@ -81,7 +81,7 @@ def test_masks_that_are_not_provably_causal_are_left_alone():
 
     k2, v2 = (torch.randn(2, 4, 128, 128).bfloat16() for _ in range(2))
     targets = _targets_after_joint_passes(longer_keys, q, k2, v2)
-    assert "b200_graph.b200_fa.default" not in targets
+    assert "b200_graph.b200_sdpa.default" not in targets
 
 
 def test_float32_attention_needs_the_opt_in():
@@ -89,10 +89,10 @@ def test_float32_attention_needs_the_opt_in():
 
     q, k, v = (torch.randn(2, 4, 64, 128) for _ in range(3))
     fn = _literal_attention("tril", "mul", 0.1)
-    assert "b200_graph.b200_fa.default" not in _targets_after_joint_passes(fn, q, k, v)
+    assert "b200_graph.b200_sdpa.default" not in _targets_after_joint_passes(fn, q, k, v)
     config.attention_fp32_as_fp16 = True
     try:
-        assert "b200_graph.b200_fa.default" in _targets_after_joint_passes(fn, q, k, v)
+        assert "b200_graph.b200_sdpa.default" in _targets_after_joint_passes(fn, q, k, v)
     finally:
         config.attention_fp32_as_fp16 = False
 

@@ -56,7 +56,8 @@ def test_c1_graph_is_one_row_kernel(dry_backend):
     assert code.count("ixb_load_kernel('''") == 1
     assert launch_shape(code) == (128, 1, 2)              # 1024 fp32 = 256 vectors
     # w and b are the same for every row: loaded once per thread; x is fetched a row ahead
-    assert code.count("k.k0 = c.load_row(") == 1 and code.count("k.k1 = c.load_row(") == 1
+    assert code.count("kinit<0, IXB_ROW_KREGS>(c, k.k0,") == 1 and code.count("kinit<1, IXB_ROW_KREGS>(c, k.k1,") == 1
+    assert "#define IXB_ROW_KREGS 2" in code             # both stay in registers at 8 elements per thread
     assert "c.fetch_row(" in code and "c.template operand<STAGED, float>(raw.s0" in code
     # x * w + b is one fused multiply-add, the decomposed exact GELU one call
     assert "ixb::gen::op::fma(" in code and "ixb::gen::op::gelu_erf(" in code
@@ -71,7 +72,10 @@ def test_c2_chain_is_one_row_kernel_with_four_reductions(dry_backend):
     assert launch_shape(code) == (256, 1, 2)              # 4096 bf16 = 512 vectors
     # two exchanges per row: the online softmax, which also carries sum(e * g) and sum(x) for
     # the LayerNorm mean, and the centred second moment
-    assert "c.template online_softmax<1, 1>(tmp1, ixb::gen::refs<kN>(k.k0), ixb::gen::refs<kN>(tmp0))" in code
+    assert ("c.template online_softmax<1, 1>(tmp1, ixb::gen::refs<kN>(ixb::gen::kget<0, IXB_ROW_KREGS>(c, k.k0)), "
+            "ixb::gen::refs<kN>(tmp0))") in code
+    # g is used twice (rider and product), so it is operand 0: the last to leave the registers
+    assert code.count("kget<0, IXB_ROW_KREGS>") == 2 and "#define IXB_ROW_KREGS 3" in code
     assert ".scaled[0]" in code and ".plain[0]" in code
     assert len(re.findall(r"c\.template reduce<", code)) == 0 and code.count("c.reduce_dot(") == 1
     # exp(x - max) / sum comes from the exponentials the exchange kept
@@ -131,6 +135,21 @@ def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backen
     # an inner-axis reduction of the same tensor keeps the row mapping
     code = generated(lambda t: t.amax(-1), x)
     assert "launch_row_gen<" in code and "launch_outer_gen" not in code
+
+
+def test_long_rows_are_walked_in_chunks(dry_backend):
+    # rows beyond MAX_TEAM x MAX_PERSISTENT_VPT vectors: one chunk loop per dependent reduction,
+    # accumulators ahead of the loop, one team exchange after it
+    code = generated(lambda t: torch.log_softmax(t, -1), torch.randn(4, 128256))
+    assert code.count("ixb_load_kernel('''") == 1
+    assert code.count("for (int chunk = 0; chunk < c.nchunks(); ++chunk)") == 2
+    assert "c.online_chunk(_acc0," in code and "c.online_finish(_acc0)" in code
+    assert "static constexpr bool kLooped = true;" in code and "tune=dict(" not in code
+    code = generated(lambda t: torch.var_mean(t, -1), torch.randn(4, 300000))
+    assert "c.local_welford(" in code or code.count("c.nchunks()") == 2
+    # a row that fits stays on chip
+    code = generated(lambda t: torch.log_softmax(t, -1), torch.randn(4, 32768))
+    assert "c.nchunks()" not in code and "static constexpr bool kLooped = false;" in code
 
 
 def test_index_analysis_is_structural():
