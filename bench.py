@@ -189,9 +189,12 @@ class SoftmaxLayerNorm(Workload):
             self.compiled_into = torch.compile(lambda x, g, ga, be, out: out.copy_(fn(x, g, ga, be)), dynamic=False)
         return self.compiled_into(x, *self.params, out)
 
-    def e2e_setup(self, device, chunks=8):
+    e2e_chunks = 8     # fewer, larger chunks when several ranks share the host's copy engines
+
+    def e2e_setup(self, device, chunks=None):
         from inductor_x_b200.host_io import HostRowPipeline
 
+        chunks = chunks or self.e2e_chunks
         self.h_x = self.host["x"].pin_memory()
         self.h_y = torch.empty_like(self.h_x).pin_memory()
         self.pipe = HostRowPipeline(device, self.h_x.shape, self.h_x.dtype, self.h_x.shape,
@@ -611,13 +614,74 @@ class CpMerge(Workload):
         return fn, self.algorithmic_bytes(), "full workload, eager PyTorch on CPU (the reference's forward_update)"
 
 
+class PermutedPointwise(Workload):
+    """x[8,8,512,128] fp16 -> (x.permute(0,2,1,3) + 1).contiguous(): a permuted pointwise copy whose
+    innermost axis is kept (128-bit access on both sides).  64 copies of the tensor per step
+    (a [64,8,8,512,128] batch) so that one step moves 1 GiB."""
+
+    name = "permute_0213_f16_64x8x8x512x128"
+    dtype = "f16"
+    shape = (64 * 8, 8, 512, 128)
+    perm = (0, 2, 1, 3)
+    shard_axis = "batch"
+
+    def algorithmic_bytes(self):
+        n = 1
+        for d in self.shape:
+            n *= d
+        return 2 * n * 2
+
+    def load_host(self, seed):
+        g = torch.Generator().manual_seed(seed)
+        self.host = (torch.rand(*self.shape, generator=g) * 2 - 1).half()
+        return self.host
+
+    def setup(self, device, seed, n_sets=2):
+        x = self.load_host(seed).to(device)
+        self.xs = [x] + [x.clone() for _ in range(n_sets - 1)]
+
+    def args(self, i):
+        return (self.xs[i % len(self.xs)],)
+
+    def graph(self):
+        perm = self.perm
+        return lambda t: (t.permute(*perm) + 1.0).contiguous()
+
+    def prebuilt(self, x):
+        raise SystemExit("permuted pointwise graphs exist only in compiled form")
+
+    def e2e_setup(self, device):
+        self.h_x = self.host.pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+        self.h_o = torch.empty(self.host.numel(), dtype=torch.float16).pin_memory()
+
+    def e2e_step(self):
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        self.h_o.copy_(self.op(self.d_x).reshape(-1), non_blocking=True)
+        return self.h_x.numel() * 2, self.h_o.numel() * 2
+
+    def cpu_sample(self, n=32):
+        x = self.host[:n]
+        perm = self.perm
+        fn = lambda: (x.permute(*perm) + 1.0).contiguous()
+        return fn, 2 * x.numel() * 2, f"{n} of {self.shape[0]} outer slabs, eager PyTorch"
+
+
+class TransposedPointwise(PermutedPointwise):
+    """The same tensor with its two innermost axes swapped, (0,1,3,2): a true transpose - loads
+    contiguous along one digit of the output index, stores along another."""
+
+    name = "transpose_0132_f16_64x8x8x512x128"
+    perm = (0, 1, 3, 2)
+
+
 WORKLOADS = {
     "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
     "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention,
-    "c5": LlamaLayer, "cp": CpMerge,
+    "c5": LlamaLayer, "cp": CpMerge, "perm": PermutedPointwise, "transpose": TransposedPointwise,
 }
 #: configurations reported under `configs` after the headline: (key, steps per replay, replays floor)
-SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "c4", "c5")
+SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "perm", "transpose", "c4", "c5")
 
 
 # ---------------------------------------------------------------------------- driver
@@ -963,6 +1027,10 @@ def main():
         wl.name = wl.name.replace("_b8_", f"_b{args.c4_batch}_")
     wl.setup(env.device, seed=env.rank)  # each rank owns a different shard of the global batch
     wl.bind(args.path)
+    if isinstance(wl, SoftmaxLayerNorm):
+        # every rank drives its own pinned staging pair; with several ranks on one host the copy
+        # engines and the host memory system are shared, and fewer, larger chunks waste less
+        wl.e2e_chunks = {1: 8, 2: 4}.get(env.world, 2)
 
     sampler = ClockSampler(env.local_rank)
     if env.rank == 0:
@@ -1004,7 +1072,8 @@ def main():
             for key in SECONDARY:
                 try:
                     steps = {"c4": 4, "c5": 3}.get(key, 40)
-                    configs.append(run_config(env, key, args, args.path if key != "c5" else "compiled",
+                    configs.append(run_config(env, key, args,
+                                              args.path if key not in ("c5", "perm", "transpose") else "compiled",
                                               steps=steps, min_seconds=0.3, e2e_steps=2))
                 except Exception as e:      # one configuration failing must not lose the line
                     configs.append({"workload": key, "error": f"{type(e).__name__}: {e}"[:300]})

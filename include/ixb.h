@@ -69,8 +69,7 @@ typedef enum ixb_family {
   IXB_FAM_ROW = 1,       /* reduced axis is stride-1 and held on chip */
   IXB_FAM_OUTER = 2,     /* reduced axis is not stride-1 */
   IXB_FAM_SHORT_ROW = 3, /* stride-1 reduced axis of <= 512 bytes, permuted store */
-  IXB_FAM_GATHER = 4,
-  IXB_FAM_TRANSPOSE = 5
+  IXB_FAM_GATHER = 4
 } ixb_family;
 
 /* Device facts the launch chooser works from; replaces num_vector_core / npu_block of
@@ -264,6 +263,25 @@ int ixb_cp_forward_update_lse(float* prev_attn, float* prev_lse, const float* cu
  * gradient accumulation of the ring backward (backward_update,
  * test/npu_indexing/written/test_attn_cp.py:267-287).  numel*elsize a multiple of 16. */
 int ixb_cp_accumulate(int dtype, void* acc, const void* cur, int64_t numel, ixb_stream stream);
+
+/* ---- generated modules ------------------------------------------------------------------
+ * Every module the code generator builds (one per fused node group, compiled with nvcc for
+ * sm_100a and cached as a shared object) exports the same two C symbols; they are what the
+ * reference's launcher closure `launcher(*args, grid, stream)`
+ * (inductor_x/npu_triton_heuristics.py:239-253) becomes.  They are not symbols of libixb.so,
+ * so they are given here as function-pointer types for a host that loads such a module itself:
+ *
+ *   launch : ptrs = the tensor arguments in call order (device pointers), ints = the size
+ *            arguments in call order followed by the kept extent (and, for a row kernel with a
+ *            run-time reduced extent, that extent), stream = cudaStream_t.  Returns 0 or a
+ *            cudaError_t value; enqueues and returns.
+ *   bounds : only in modules generated with bounds checks (debug builds): copies out and
+ *            clears {number of out-of-range data-dependent indices, one offending value};
+ *            synchronises the device.  Returns 0 or a cudaError_t value. */
+typedef int (*ixb_gen_launch_fn)(void** ptrs, const long long* ints, void* stream);
+typedef int (*ixb_gen_bounds_fn)(unsigned long long* out);
+#define IXB_GEN_LAUNCH_SYMBOL "ixb_gen_launch"
+#define IXB_GEN_BOUNDS_SYMBOL "ixb_gen_bounds"
 
 #ifdef __cplusplus
 }

@@ -98,6 +98,9 @@ def register():
     _inductor_register_device_op_overrides()
     _register_device_interface()
     _enable_online_softmax_pattern()
+    from .codegen.ir import install_num_splits
+
+    install_num_splits()
     _register_b200_inductor_fallbacks()
     _register_b200_inductor_decompositions()
     from . import fusion_attention_graph

@@ -26,6 +26,47 @@ from typing import Dict, Iterable, Optional, Sequence
 import sympy
 
 
+def num_splits(*args, **kwargs):
+    """Replacement of ``torch._inductor.ir.Reduction.num_splits``
+    (``inductor_x/codegen/ir.py:13-24`` forces one split everywhere).  Inductor cuts a long
+    reduction with few outputs into two kernels through a scratch tensor.  The outer template
+    covers that case on chip - a cluster of CTAs per tile, partials combined through
+    distributed shared memory - so the cut is kept only where the kept extent is too small to
+    spread over the GPU even with clusters (a handful of outputs), or when
+    ``config.allow_multilayer_reduction`` asks for the stock behaviour."""
+    from torch._inductor.virtualized import V
+
+    from .. import config
+
+    hint, split = _stock_num_splits(*args, **kwargs)
+    if config.allow_multilayer_reduction or kwargs.get("reduction_type", args[6] if len(args) > 6 else None) == "scan":
+        return hint, split
+    try:
+        ranges = kwargs.get("ranges", args[4] if len(args) > 4 else ())
+        device = kwargs.get("device", args[0] if args else None)
+        kept = 1
+        for r in ranges:
+            kept *= int(V.graph.sizevars.size_hint(r))
+        if getattr(device, "type", None) == "cuda" and int(split) > 1 and kept >= config.min_kept_for_single_kernel:
+            return hint, 1
+    except Exception:
+        pass
+    return hint, split
+
+
+_stock_num_splits = None
+
+
+def install_num_splits():
+    """Patch ``Reduction.num_splits`` once (kept callable as a static method)."""
+    global _stock_num_splits
+    from torch._inductor import ir as inductor_ir
+
+    if _stock_num_splits is None:
+        _stock_num_splits = inductor_ir.Reduction.num_splits
+        inductor_ir.Reduction.num_splits = staticmethod(num_splits)
+
+
 def expand_to_roots(index: sympy.Expr, range_tree_nodes: Dict[sympy.Symbol, object]) -> sympy.Expr:
     """Rewrite ``index`` so that only root index symbols (``xindex``, ``r0_index`` ...) and
     non-range symbols remain.  ``range_tree_nodes`` maps entry symbols to entries whose

@@ -363,6 +363,11 @@ class B200Kernel(SIMDKernel):
         if not self.is_row:
             line = gather.replace("@M@", "xmask")
             xsym = self._root("x").symbol()
+            if not indirect and not masked:
+                exp0 = self._expanded(index)
+                if xsym in exp0.free_symbols and not index_ir.is_vector_constant(exp0, xsym, self.vec) and \
+                        not index_ir.vector_access(exp0, xsym, self.vec)[0]:
+                    self.__dict__.setdefault("_gather_loads", []).append(exp0)   # strided: a transpose candidate
             if indirect and not masked:
                 # direct part contiguous along the vector: one 128-bit access whenever the
                 # indirect operands are per-vector scalars (decided by their C++ type)
@@ -415,7 +420,7 @@ class B200Kernel(SIMDKernel):
                     self._row_prefetch.append(row_ptr)     # streamed once per row: worth prefetching
                 aligned = index_ir.row_starts_aligned(exp, xr.symbol(), rr.symbol(), cfg.vec) and \
                     not self._is_dynamic("r0_") and self._numel_hint("r0_") % cfg.vec == 0
-                if narrow_ok and aligned and cfg.team >= 32 and not self.looped:
+                if narrow_ok and aligned and not self.looped:
                     member = next((m for m, _, ptr in self.staged if ptr == row_ptr), None)
                     if member is None and len(self.staged) < MAX_STAGED:
                         member = f"raw.s{len(self.staged)}"
@@ -886,6 +891,76 @@ class B200Kernel(SIMDKernel):
             cs *= 2
         return (tx, cs) if cs > 1 else (self._outer_tx(), 1)
 
+    def _transposing_order(self):
+        """Constants of the lane order for a pointwise kernel whose stores are contiguous along
+        the flat index but whose strided loads are contiguous along another digit C of it (a
+        transpose): consecutive lanes of a warp then step along C, so that each of the V scalar
+        loads of a thread is one coalesced request across the warp, while every thread still
+        stores one 128-bit vector along the flat index.  This is the job of the reference's
+        second set of index variables and ``.permute(1, 0)`` on the tile
+        (``inductor_x/codegen/triton.py:856-888, 1303-1332``), done here by the walking order
+        alone - the sectors a warp touches on both sides are fully used, without a shared-memory
+        tile.  Returns (LB, dC, LC) or None."""
+        if self.is_row or self._is_dynamic("x") or not getattr(self, "_gather_loads", None):
+            return None
+        xsym = self._root("x").symbol()
+        xnumel = self._numel_hint("x")
+        found = None
+        for exp in self._gather_loads:
+            split = index_ir._axis_pieces(exp, xsym)
+            if split is None or split[0].free_symbols:
+                return None
+            unit = [(c, d, m) for c, d, m in split[1] if c == 1 and d > 1]
+            low = [(c, d, m) for c, d, m in split[1] if d == 1]
+            if len(unit) != 1 or len(low) != 1 or low[0][2] is None:
+                return None
+            lb, (_, dc, lc) = low[0][2], unit[0]
+            if lc is None:
+                lc = xnumel // dc
+            if dc % lb or xnumel % (dc * lc) or lc % 32 or lb % self.vec:
+                return None
+            if found is not None and found != (lb, dc, lc):
+                return None
+            found = (lb, dc, lc)
+        return found
+
+    def _short_row_tiling(self):
+        """(LB, LC) when the kept index of a short-row kernel should be walked in tiles: the
+        kept space is [..][LC][LB] with LB fastest (the output's order), every streamed row
+        operand has rows adjacent in memory along the LC digit and far apart along LB, and the
+        per-row results are contiguous along LB.  None otherwise."""
+        if self.looped or self._is_dynamic("x") or self._is_dynamic("r0_"):
+            return None
+        xr, rr = self._xr_roots()
+        rnumel = self._static_numel("r0_")
+        if rnumel * config_bytes(self._narrowest_node_dtype()) > 512:
+            return None
+        loads = [v for v in self._ph.values() if v["kind"] == "L" and v["has_r"] and not v["indirect"]]
+        if not loads or any(v["stride"] != 1 for v in loads):
+            return None
+        found = None
+        for v in loads:
+            split = index_ir._axis_pieces(v["exp"].subs({rr.symbol(): 0}), xr.symbol())
+            if split is None:
+                return None
+            pieces = {d: (c, m) for c, d, m in split[1]}
+            if 1 not in pieces or pieces[1][1] is None:
+                return None
+            lb = pieces[1][1]
+            if lb not in pieces:
+                return None
+            coef_c, lc = pieces[lb]
+            if lc is None:
+                lc = self._numel_hint("x") // lb       # the outermost digit: FloorDiv without modulus
+                if self._numel_hint("x") != lb * lc:
+                    return None
+            if coef_c != rnumel or pieces[1][0] < coef_c * lc or lb % 16 or lc % 16:
+                return None
+            if found is not None and found != (lb, lc):
+                return None
+            found = (lb, lc)
+        return found
+
     def _substitute(self, text: str, outer: bool) -> str:
         for tag, v in self._ph.items():
             if v.get("online") and not outer:
@@ -965,6 +1040,9 @@ class B200Kernel(SIMDKernel):
                 import re
 
                 cfg = self._row_cfg
+                tiling = self._short_row_tiling()
+                slot_line = ("const long long xindex = xslot;" if tiling is None else
+                             f"const long long xindex = {G}tile_order<{tiling[0]}, {tiling[1]}, 16, 16>(xslot);")
                 row_body = re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False))
                 # per-column operands, most used first: the first IXB_ROW_KREGS of them are
                 # registers, the others are read from the shared-memory table
@@ -999,9 +1077,10 @@ class B200Kernel(SIMDKernel):
                 src.writeline("}")
                 # raw vectors of the streamed operands of one row (requested a row ahead)
                 src.writeline("template <class Ctx>")
-                src.writeline("__device__ __forceinline__ void fetch(Ctx& c, const long long xindex, Raw& raw) const {")
+                src.writeline("__device__ __forceinline__ void fetch(Ctx& c, const long long xslot, Raw& raw) const {")
                 with src.indent():
                     if self.staged:
+                        src.writeline(slot_line)
                         src.writeline("const auto r0_index = c.rindex();")
                         src.splice(x_idx)
                         src.splice(r_idx)
@@ -1009,9 +1088,10 @@ class B200Kernel(SIMDKernel):
                             src.writeline(f"c.fetch_row({ptr}, {member});")
                 src.writeline("}")
                 src.writeline("template <bool STAGED, class Ctx>")
-                src.writeline("__device__ __forceinline__ void row(Ctx& c, const Consts& k, const long long xindex, "
+                src.writeline("__device__ __forceinline__ void row(Ctx& c, const Consts& k, const long long xslot, "
                               "const Raw& raw) const {")
                 with src.indent():
+                    src.writeline(slot_line)
                     if self.looped:
                         src.splice(x_idx)        # the reduced index is defined inside each chunk loop
                     else:
@@ -1023,9 +1103,10 @@ class B200Kernel(SIMDKernel):
                 src.writeline("}")
                 # L2 prefetch of the streamed operands of a later row
                 src.writeline("template <class Ctx>")
-                src.writeline("__device__ __forceinline__ void prefetch(Ctx& c, const long long xindex) const {")
+                src.writeline("__device__ __forceinline__ void prefetch(Ctx& c, const long long xslot) const {")
                 with src.indent():
                     if self._row_prefetch:
+                        src.writeline(slot_line)
                         src.writeline("const auto r0_index = c.rindex();")
                         src.splice(x_idx)
                         src.splice(r_idx)
@@ -1034,6 +1115,24 @@ class B200Kernel(SIMDKernel):
                 src.writeline("}")
             else:
                 src.writeline(f"static constexpr int kVec = {self.vec};")
+                order = self._transposing_order()
+                src.writeline("__device__ __forceinline__ long long first_of(long long slot) const {")
+                with src.indent():
+                    if order is None:
+                        src.writeline("return slot * kVec;")
+                    else:
+                        lb, dc, lc = order
+                        nbv = lb // self.vec
+                        tbv = next(t for t in (8, 4, 2, 1) if nbv % t == 0)
+                        src.writeline("// lanes along the digit the loads are contiguous in, vectors along the flat index")
+                        src.writeline("const long long c_lo = slot % 32; long long t = slot / 32;")
+                        src.writeline(f"const long long bv_lo = t % {tbv}; t /= {tbv};")
+                        src.writeline(f"const long long bv_hi = t % {nbv // tbv}; t /= {nbv // tbv};")
+                        src.writeline(f"const long long mid = t % {dc // lb}; t /= {dc // lb};")
+                        src.writeline(f"const long long c_hi = t % {lc // 32}; t /= {lc // 32};")
+                        src.writeline(f"return (bv_hi * {tbv} + bv_lo) * kVec + mid * {lb}LL + (c_hi * 32 + c_lo) * {dc}LL "
+                                      f"+ t * {dc * lc}LL;")
+                src.writeline("}")
                 src.writeline("template <bool FAST>")
                 src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid) const {")
                 with src.indent():

@@ -111,9 +111,19 @@ def row_candidates(rnumel: int, chosen: RowConfig, rows: Optional[int] = None, n
     (``codegen/jit.py``)."""
     vec = chosen.vec
     nvec = -(-rnumel // vec)
-    if chosen.team < 32:
-        return []                         # rows of a few vectors: the static choice stands
     default = (chosen.team, chosen.teams, chosen.vpt, chosen.min_ctas, chosen.prefetch, kregs)
+    if chosen.team < 32:
+        # rows of a few vectors: fewer lanes per row with more vectors each (shorter shuffle
+        # trees, less index arithmetic per byte) against fully coalesced single vectors
+        out = []
+        for vpt in (2, 4):
+            team = nvec // vpt
+            if team < 2 or team * vpt != nvec or team & (team - 1):
+                continue
+            shape = (team, 128 // team, vpt, chosen.min_ctas, chosen.prefetch, kregs)
+            if shape != default:
+                out.append(shape)
+        return out
     ranked = []
     for vpt in (1, 2, 4):
         team = 32

@@ -14,9 +14,12 @@ register_on_import = os.environ.get("IXB_REGISTER", "1") != "0"
 #: print ms / GB / GB/s for every generated kernel launch (the reference's
 #: NPUDebugAutotuner, inductor_x/npu_triton_heuristics.py:268-299)
 profile_bandwidth = os.environ.get("IXB_PROFILE_BANDWIDTH", "0") == "1"
-#: keep Inductor's own multi-layer split of long reductions (the reference forces
-#: num_splits == 1, inductor_x/codegen/ir.py:13-24)
-allow_multilayer_reduction = True
+#: keep Inductor's own two-kernel split of long reductions everywhere (the reference forces
+#: num_splits == 1, inductor_x/codegen/ir.py:13-24).  Off: a reduction with at least
+#: ``min_kept_for_single_kernel`` outputs stays one kernel and is split over a thread-block
+#: cluster on chip instead.
+allow_multilayer_reduction = os.environ.get("IXB_MULTILAYER_REDUCTION", "0") == "1"
+min_kept_for_single_kernel = 32
 #: one exchange for LayerNorm-style (mean, m2) statistics by merging partial statistics.
 #: Off by default: on the bf16 softmax->LayerNorm chain at 16384 x 4096 the merged form
 #: measured slower (106 us -> 151 us) - the divisions of the merge cost more than the

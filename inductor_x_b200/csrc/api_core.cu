@@ -176,7 +176,6 @@ int ixb_choose_config(const ixb_problem* pb, const ixb_devinfo* dev, ixb_cfg* ou
       return IXB_OK;
     }
     case IXB_FAM_POINTWISE:
-    case IXB_FAM_TRANSPOSE:
       out->threads = 256;
       out->unroll = 4;
       return IXB_OK;

@@ -277,7 +277,9 @@ __global__ void __launch_bounds__(256) pointwise_gen_kernel(const Body body, con
   const long long ntiles = (xnumel + V - 1) / V;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < ntiles; t += stride) {
-    const long long xbase = t * V;
+    // Body::first_of maps the thread's slot to the first element of its vector: t * V, or the
+    // transposing order (consecutive lanes along the axis the loads are contiguous in)
+    const long long xbase = body.first_of(t);
     const long long left = xnumel - xbase;
     if (ALIGNED && left >= V) body.template tile<true>(xbase, V);
     else body.template tile<false>(xbase, left >= V ? V : (int)left);
@@ -932,6 +934,25 @@ __device__ __forceinline__ vf<E> kget(const Ctx& c, const vf<E>& reg) {
   else return c.template sconst<J - KREGS>();
 }
 
+// Order in which a row kernel with short rows walks its kept index.  The kept space is
+// [A][LC][LB] with LB fastest (the order of the output), while the rows that are adjacent in
+// memory are the ones that differ in the LC digit.  Walking it in TB x TC tiles - TC consecutive
+// LC digits fastest, then TB consecutive LB digits - makes a warp read adjacent rows (one
+// contiguous span) and lets the one-element-per-row results of a tile fill whole sectors, the
+// job the reference gives its transposed tile (inductor_x/codegen/triton.py:856-888).
+template <int LB, int LC, int TB, int TC>
+__device__ __forceinline__ long long tile_order(long long slot) {
+  static_assert(LB % TB == 0 && LC % TC == 0, "tiles must divide both extents");
+  constexpr long long kPlane = (long long)LB * LC;
+  const long long a = slot / kPlane;
+  const int rem = (int)(slot % kPlane);
+  const int c_lo = rem % TC;
+  const int b_lo = (rem / TC) % TB;
+  const int b_hi = (rem / (TC * TB)) % (LB / TB);
+  const int c_hi = rem / (TC * LB);
+  return a * kPlane + (long long)(c_hi * TC + c_lo) * LB + (b_hi * TB + b_lo);
+}
+
 // CTAs of a row kernel that fit on one SM, cached per device (the attribute is a property of
 // the device the calling thread has current; several host threads may ask at once)
 template <class K> inline int row_resident(K kern, int threads, size_t smem = 0) {
@@ -974,14 +995,27 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   if constexpr (Body::kSmemConsts > 0) __syncthreads();   // the operand table is complete
   const long long stride = (long long)gridDim.x * TEAMS;
   if constexpr (TEAM < 32) {
-    // the teams of a warp run the same number of rows (full-mask shuffles inside)
-    typename Body::Raw raw;
-    for (long long base = (long long)blockIdx.x * TEAMS; base < rows; base += stride) {
-      const long long r = base + c.team;
-      c.live = r < rows;
-      const long long rr = c.live ? r : rows - 1;
-      if constexpr (STAGED) body.fetch(c, rr, raw);
-      body.template row<STAGED>(c, k, rr, raw);
+    // The teams of a warp run the same number of rows (full-mask shuffles inside).  Rows this
+    // short give a thread one vector each, so kBatch rows are fetched before the first is
+    // worked on: kBatch independent loads in flight per thread instead of one.
+    constexpr int kBatch = STAGED ? 4 : 1;
+    typename Body::Raw raw[kBatch];
+    for (long long base = (long long)blockIdx.x * TEAMS; base < rows; base += stride * kBatch) {
+      if constexpr (STAGED) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const long long r = base + u * stride + c.team;
+          body.fetch(c, r < rows ? r : rows - 1, raw[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const long long b = base + u * stride;
+        if (b >= rows) break;            // uniform over the CTA
+        const long long r = b + c.team;
+        c.live = r < rows;
+        body.template row<STAGED>(c, k, c.live ? r : rows - 1, raw[u]);
+      }
     }
     return;
   } else {

@@ -27,8 +27,7 @@ IXB_ERR_UNSUPPORTED, IXB_ERR_SCRATCH, IXB_ERR_CUDA, IXB_ERR_INDEX = 5, 6, 7, 8
 
 IXB_F32, IXB_F16, IXB_BF16, IXB_I64, IXB_I32, IXB_U8 = 0, 1, 2, 3, 4, 5
 IXB_SUM, IXB_MEAN, IXB_AMAX, IXB_AMIN, IXB_ARGMAX, IXB_ARGMIN, IXB_VAR_MEAN = range(7)
-(IXB_FAM_POINTWISE, IXB_FAM_ROW, IXB_FAM_OUTER, IXB_FAM_SHORT_ROW, IXB_FAM_GATHER,
- IXB_FAM_TRANSPOSE) = range(6)
+(IXB_FAM_POINTWISE, IXB_FAM_ROW, IXB_FAM_OUTER, IXB_FAM_SHORT_ROW, IXB_FAM_GATHER) = range(5)
 
 DTYPE_CODE = {
     torch.float32: IXB_F32,
