@@ -198,27 +198,48 @@ class B200Kernel(SIMDKernel):
             return True                  # run-time extent: persistent up to the compiled capacity
         vec = min(max(ixb_config.get_aligned_numel(self._narrowest_node_dtype()), 1), 8)
         nvec = -(-rnumel // vec)
-        self.looped = nvec > split_tiling.MAX_TEAM * split_tiling.MAX_PERSISTENT_VPT and not self._reads_are_strided()
+        long_row = nvec > split_tiling.MAX_TEAM * split_tiling.MAX_PERSISTENT_VPT
+        try:
+            kept = int(self.features.numel)
+        except TypeError:
+            kept = vec
+        # a strided (outer) reduction is served by the outer mapping, which needs at least one
+        # vector of kept elements; anything else that long is walked in chunks
+        self.looped = long_row and not (kept >= vec and self._reads_are_strided())
         return not self.looped
 
     def _reads_are_strided(self) -> bool:
         """True when no read of a reduction node walks a reduced variable with stride 1: an
-        outer reduction (decided from the scheduler nodes, before any code is emitted)."""
+        outer reduction (decided from the scheduler nodes, before any code is emitted).  The
+        reduced variables of a dependency are its trailing loop variables whose extents
+        multiply to the reduced extent."""
         from torch._inductor.dependencies import MemoryDep
 
+        try:
+            rnumel = int(self.features.reduction_numel)
+        except TypeError:
+            return False
         saw = False
         for node in self.features.scheduler_nodes():
             if not node.is_reduction():
                 continue
-            body = getattr(node, "_body", None)
-            reduce_vars = set(getattr(body, "reduce_vars", ()) or ())
             for dep in node.read_writes.reads:
-                if not isinstance(dep, MemoryDep):
+                if not isinstance(dep, MemoryDep) or not dep.var_names:
                     continue
-                rvars = [v for v in dep.var_names if v in reduce_vars] if reduce_vars else list(dep.var_names[-1:])
+                prod, rvars = 1, []
+                for v, size in zip(reversed(dep.var_names), reversed(dep.size)):
+                    if prod >= rnumel:
+                        break
+                    try:
+                        prod *= int(size)
+                    except TypeError:
+                        return False
+                    rvars.append(v)
+                if prod != rnumel:
+                    continue             # this dependency does not span the reduced axis in its loop nest
                 rvars = [v for v in rvars if v in dep.index.free_symbols]
                 if not rvars:
-                    continue
+                    continue             # broadcast along the reduced axis
                 saw = True
                 strides = V.graph.sizevars.stride_vars(dep.index, rvars)
                 if any(st == 1 for st in strides):
@@ -367,7 +388,14 @@ class B200Kernel(SIMDKernel):
                 exp0 = self._expanded(index)
                 if xsym in exp0.free_symbols and not index_ir.is_vector_constant(exp0, xsym, self.vec) and \
                         not index_ir.vector_access(exp0, xsym, self.vec)[0]:
-                    self.__dict__.setdefault("_gather_loads", []).append(exp0)   # strided: a transpose candidate
+                    # strided along the flat index: a transpose candidate; the text is settled
+                    # when the whole group has been seen (register tile or per-element gather)
+                    loads = self.__dict__.setdefault("_gather_loads", [])
+                    loads.append(exp0)
+                    tag = f"@T{len(loads) - 1}@"
+                    self.__dict__.setdefault("_tile_loads", {})[tag] = dict(
+                        ctype=ctype, dtype=dtype, var=var, idx=idx, exp=exp0, gather=line)
+                    return self.cse.generate(self.compute, tag, dtype=val_dtype)
             if indirect and not masked:
                 # direct part contiguous along the vector: one 128-bit access whenever the
                 # indirect operands are per-vector scalars (decided by their C++ type)
@@ -924,6 +952,32 @@ class B200Kernel(SIMDKernel):
             found = (lb, dc, lc)
         return found
 
+    def _register_tile(self, order):
+        """kC (elements per 128-bit load along C) when every strided load of the group can be
+        staged as a register tile under the transposing order ``order``: one storage width, rows
+        of the tile 16-byte aligned by construction, extents that the 4 x 8 lane arrangement
+        divides.  None keeps the per-element gathers."""
+        tl = getattr(self, "_tile_loads", None)
+        if order is None or not tl:
+            return None
+        lb, dc, lc = order
+        sizes = {config_bytes(v["dtype"]) for v in tl.values()}
+        if len(sizes) != 1 or not all(v["dtype"] in (torch.float32, torch.float16, torch.bfloat16) for v in tl.values()):
+            return None
+        kc = 16 // sizes.pop()
+        xsym = self._root("x").symbol()
+        nbv = lb // self.vec
+        if lc % (kc * 8) or nbv % 4:
+            return None
+        for v in tl.values():
+            _, pieces = index_ir._axis_pieces(v["exp"], xsym)
+            rest = index_ir._axis_pieces(v["exp"], xsym)[0]
+            if not rest.is_Integer or int(rest) % kc:
+                return None
+            if any(c % kc for c, d, m in pieces if not (c == 1 and d == dc)):
+                return None
+        return kc
+
     def _short_row_tiling(self):
         """(LB, LC) when the kept index of a short-row kernel should be walked in tiles: the
         kept space is [..][LC][LB] with LB fastest (the output's order), every streamed row
@@ -978,6 +1032,11 @@ class B200Kernel(SIMDKernel):
         x_idx, r_idx = self.x_indexing.getvalue(), self.r_indexing.getvalue()
         outer = self.is_row and self._choose_outer(body_text)
         self.mapping = "outer" if outer else ("row" if self.is_row else "pointwise")
+        if self.mapping == "row" and not self.looped and not self._is_dynamic("r0_") and \
+                self._static_numel("r0_") > self._row_cfg.capacity:
+            raise UnsupportedByTemplates(
+                f"a strided reduction over {self._static_numel('r0_')} elements that the outer template cannot "
+                "take (several reductions or values shared across the reduction loop)")
 
         src = IndentedBuffer()
         if self.checked_indices:
@@ -1116,6 +1175,41 @@ class B200Kernel(SIMDKernel):
             else:
                 src.writeline(f"static constexpr int kVec = {self.vec};")
                 order = self._transposing_order()
+                kc = self._register_tile(order)
+                tile_loads = getattr(self, "_tile_loads", {})
+                for n, (tag, v) in enumerate(tile_loads.items()):
+                    text = v["gather"] if kc is None else f"(STAGED ? {G}take(raw.t{n}, ci) : {v['gather']})"
+                    body_text = body_text.replace(tag, text)
+                if kc is not None:
+                    lb, dc, lc = order
+                    nbv = lb // self.vec
+                    src.writeline(f"static constexpr int kTileC = {kc};          // elements per 128-bit load along the loads' axis")
+                    src.writeline(f"static constexpr long long kStepC = {dc}LL;   // flat-index distance between output vectors of a tile")
+                    src.writeline("struct Tile {")
+                    with src.indent():
+                        for n, v in enumerate(tile_loads.values()):
+                            src.writeline(f"{G}TileRaw<{v['ctype']}, kVec> t{n};")
+                    src.writeline("};")
+                    src.writeline("__device__ __forceinline__ long long first_of_tile(long long slot) const {")
+                    with src.indent():
+                        src.writeline("// lanes: 4 vectors along the flat index by 8 tiles along the loads' axis")
+                        src.writeline("const long long bv_lo = slot % 4; long long t = slot / 4;")
+                        src.writeline("const long long c_lo = t % 8; t /= 8;")
+                        src.writeline(f"const long long bv_hi = t % {nbv // 4}; t /= {nbv // 4};")
+                        src.writeline(f"const long long mid = t % {dc // lb}; t /= {dc // lb};")
+                        src.writeline(f"const long long c_hi = t % {lc // (kc * 8)}; t /= {lc // (kc * 8)};")
+                        src.writeline(f"return (bv_hi * 4 + bv_lo) * kVec + mid * {lb}LL + (c_hi * 8 + c_lo) * {kc * dc}LL "
+                                      f"+ t * {dc * lc}LL;")
+                    src.writeline("}")
+                    src.writeline("__device__ __forceinline__ void fetch_tile(const long long xbase, Tile& raw) const {")
+                    with src.indent():
+                        src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
+                        src.splice(x_idx)
+                        for n, v in enumerate(tile_loads.values()):
+                            src.writeline(f"{G}fetch_tile(raw.t{n}, {v['var']}, {v['idx']});")
+                    src.writeline("}")
+                else:
+                    src.writeline("struct Tile {};")
                 src.writeline("__device__ __forceinline__ long long first_of(long long slot) const {")
                 with src.indent():
                     if order is None:
@@ -1133,8 +1227,9 @@ class B200Kernel(SIMDKernel):
                         src.writeline(f"return (bv_hi * {tbv} + bv_lo) * kVec + mid * {lb}LL + (c_hi * 32 + c_lo) * {dc}LL "
                                       f"+ t * {dc * lc}LL;")
                 src.writeline("}")
-                src.writeline("template <bool FAST>")
-                src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid) const {")
+                src.writeline("template <bool FAST, bool STAGED = false>")
+                src.writeline("__device__ __forceinline__ void tile(const long long xbase, const int nvalid, "
+                              "const Tile& raw = Tile(), const int ci = 0) const {")
                 with src.indent():
                     src.writeline(f"const auto xindex = {G}iota<kVec>(xbase);")
                     src.writeline("const auto xmask = xindex < (xbase + nvalid);")
@@ -1176,7 +1271,8 @@ class B200Kernel(SIMDKernel):
                               f"IXB_GEN_MIN_CTAS, IXB_ROW_PF, kFull>(b, xnumel, {rnumel}, stream, "
                               f"{G}pointers_aligned(ptrs, {nptr}));")
             else:
-                src.writeline(f"return {G}launch_pointwise<Body>(b, xnumel, stream, "
+                launcher = "launch_pointwise_tile" if self._register_tile(self._transposing_order()) else "launch_pointwise"
+                src.writeline(f"return {G}{launcher}<Body>(b, xnumel, stream, "
                               f"{G}pointers_aligned(ptrs, {len([a for a in assigns if 'ptrs[' in a])}));")
         src.writeline("}")
         if self.checked_indices:

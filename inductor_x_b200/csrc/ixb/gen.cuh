@@ -285,6 +285,75 @@ __global__ void __launch_bounds__(256) pointwise_gen_kernel(const Body body, con
     else body.template tile<false>(xbase, left >= V ? V : (int)left);
   }
 }
+// ---- transposes: a register tile per thread ---------------------------------------------------
+// A pointwise group that stores along the flat index but reads an operand that is contiguous
+// along another digit C of it (a transpose) gives every thread a V x kC micro-tile of that
+// operand: V 128-bit loads, each kC consecutive elements along C (one for each of the V
+// positions of the thread's vector along the flat index), then kC output vectors - element ci
+// of every loaded row is the operand of output vector ci.  Both sides move 128 bits per access
+// and the extraction costs what widening a half would cost anyway.  Lanes are arranged 4 along
+// the flat index by 8 along C, so a warp reads four full 128-byte lines per load instruction
+// and writes 64-byte runs.  This is what the reference's second set of index variables and
+// `.permute(1, 0)` on the tile are for (inductor_x/codegen/triton.py:856-888, 1303-1332).
+template <class U, int V> struct TileRaw {
+  static constexpr int kC = 16 / (int)sizeof(U);
+  uint4 q[V];
+};
+template <class U, int V, class I>
+__device__ __forceinline__ void fetch_tile(TileRaw<U, V>& r, const U* p, const I& idx) {
+#pragma unroll
+  for (int j = 0; j < V; ++j) r.q[j] = ldg_stream(p + at(idx, j));
+}
+template <class U> __device__ __forceinline__ float tile_elem(const uint4& q, int ci);
+template <> __device__ __forceinline__ float tile_elem<float>(const uint4& q, int ci) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  return __uint_as_float(w[ci]);
+}
+template <> __device__ __forceinline__ float tile_elem<bf16>(const uint4& q, int ci) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  return __uint_as_float((ci & 1) ? (w[ci >> 1] & 0xffff0000u) : (w[ci >> 1] << 16));
+}
+template <> __device__ __forceinline__ float tile_elem<f16>(const uint4& q, int ci) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  const __half2 h = *reinterpret_cast<const __half2*>(&w[ci >> 1]);
+  return (ci & 1) ? __high2float(h) : __low2float(h);
+}
+// element ci of every row of the tile, widened: the operand of output vector ci
+template <class U, int V> __device__ __forceinline__ vf<V> take(const TileRaw<U, V>& t, int ci) {
+  vf<V> r;
+#pragma unroll
+  for (int j = 0; j < V; ++j) r.v[j] = tile_elem<U>(t.q[j], ci);
+  return r;
+}
+
+template <class Body>
+__global__ void __launch_bounds__(256) pointwise_tile_gen_kernel(const Body body, const long long xnumel) {
+  constexpr int V = Body::kVec;
+  constexpr int C = Body::kTileC;
+  const long long ntiles = xnumel / ((long long)V * C);     // exact by construction of the order
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < ntiles; t += stride) {
+    const long long x0 = body.first_of_tile(t);
+    typename Body::Tile raw;
+    body.fetch_tile(x0, raw);
+#pragma unroll
+    for (int ci = 0; ci < C; ++ci) body.template tile<true, true>(x0 + ci * Body::kStepC, V, raw, ci);
+  }
+}
+template <class Body> int launch_pointwise(const Body& body, long long xnumel, void* stream, bool aligned);
+// tiles when every pointer is 16-byte aligned, the plain kernel (per-element gathers) otherwise
+template <class Body> int launch_pointwise_tile(const Body& body, long long xnumel, void* stream, bool aligned) {
+  if (xnumel <= 0) return 0;
+  if (!aligned) return launch_pointwise(body, xnumel, stream, false);
+  static const long long cap = resident_ctas(pointwise_tile_gen_kernel<Body>, 256);
+  const long long ntiles = xnumel / ((long long)Body::kVec * Body::kTileC);
+  long long grid = (ntiles + 255) / 256;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  pointwise_tile_gen_kernel<Body><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(body, xnumel);
+  return (int)cudaGetLastError();
+}
+
 template <class Body> int launch_pointwise(const Body& body, long long xnumel, void* stream, bool aligned = false) {
   if (xnumel <= 0) return 0;
   static const long long cap_a = resident_ctas(pointwise_gen_kernel<Body, true>, 256);

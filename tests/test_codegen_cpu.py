@@ -122,6 +122,19 @@ def test_permuted_store_falls_back_to_scatter_or_gather(dry_backend):
     assert "gather(" in code or "scatter(" in code
 
 
+def test_transpose_is_staged_as_register_tiles(dry_backend):
+    """Loads contiguous along another digit of the flat index than the stores: 128-bit loads of
+    a V x kC micro-tile per thread, kC 128-bit stores, lanes 4 x 8."""
+    code = generated(lambda t: (t.permute(0, 1, 3, 2) * 2).contiguous(), torch.randn(8, 8, 512, 128).half())
+    assert "launch_pointwise_tile<Body>" in code
+    assert "static constexpr int kTileC = 8;" in code and "static constexpr long long kStepC = 512LL;" in code
+    assert "ixb::gen::fetch_tile(raw.t0, in_ptr0," in code and "STAGED ? ixb::gen::take(raw.t0, ci)" in code
+    assert "stvec<ixb::f16, kVec, FAST>" in code
+    # an innermost-preserving permute needs none of it: vector access on both sides
+    code = generated(lambda t: (t.permute(0, 2, 1, 3) + 1).contiguous(), torch.randn(8, 8, 512, 128).half())
+    assert "launch_pointwise<Body>" in code and "gather(" not in code
+
+
 def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backend):
     """Reduced axes are not innermost (reference case test_reduction_permute): adjacent
     threads must walk adjacent outputs, not the strided reduction axis."""

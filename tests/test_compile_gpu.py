@@ -74,6 +74,31 @@ def test_permute_pointwise(cuda, perm):
     assert torch.equal(out, fn(x))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape,perm,tiled", [((4, 8, 512, 128), (0, 1, 3, 2), True), ((6, 256, 512), (0, 2, 1), True),
+                                              ((8, 8, 64, 128), (3, 2, 1, 0), False), ((3, 40, 72), (0, 2, 1), False)])
+def test_transposes_use_register_tiles(cuda, dtype, shape, perm, tiled):
+    """A pointwise group that stores along the flat index and reads along another digit of it:
+    every thread loads a V x kC micro-tile with 128-bit loads and stores kC 128-bit vectors
+    (where the extents allow; the last two shapes do not and keep per-element gathers).
+    Copies must be bit-exact."""
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g).to(dtype).to(cuda)
+    fn = lambda t: (t.permute(*perm) * 2.0).contiguous()
+    out, code = compile_and_code(fn, x)
+    assert torch.equal(out, fn(x))
+    assert ("launch_pointwise_tile<Body>" in code and "take(raw.t0, ci)" in code) == tiled
+    # a second operand in the output's layout rides along as an ordinary vector load
+    y = torch.randn(*out.shape, generator=g).to(dtype).to(cuda)
+    fn2 = lambda t, u: (t.permute(*perm) + u).contiguous()
+    out2, _ = compile_and_code(fn2, x, y)
+    assert torch.equal(out2, fn2(x, y))
+    # a misaligned base pointer takes the plain kernel of the same module
+    xo = torch.randn(x.numel() + 1, generator=g).to(dtype).to(cuda)[1:].view(*shape)
+    out3, _ = compile_and_code(fn, xo)
+    assert torch.equal(out3, fn(xo))
+
+
 def test_c3a_permuted_reductions(cuda):
     x = inputs.c3a((8, 16, 64, 64), seed=2)["x"].to(cuda)
     amax, _ = compile_and_code(lambda t: t.permute(0, 2, 1, 3).amax(1), x)
