@@ -253,7 +253,8 @@ def compile_source(src: str, verbose: bool = False, shape=None) -> str:
         bounds = [n]          # a candidate is built exactly as named; one that spills is dropped
     for bound in bounds:
         extra = [] if bound is None else [f"-DIXB_GEN_MIN_CTAS={bound}"]
-        cmd = ["nvcc", *_NVCC_FLAGS, "-Xptxas", "-v", *defines, *extra, "-I", _CSRC, "-o", tmp, cu]
+        cmd = ["nvcc", *_NVCC_FLAGS, "-Xptxas", "-v", *defines, *extra, *os.environ.get("IXB_NVCC_EXTRA", "").split(),
+               "-I", _CSRC, "-o", tmp, cu]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed for generated kernel {cu}:\n{proc.stderr[-4000:]}")

@@ -168,7 +168,8 @@ __device__ __forceinline__ void scatter_add(T* p, const I& idx, const M& mask, c
 // FAST: the caller knows the run is complete and 16-byte aligned (full tile, aligned base
 // pointer checked on the host, index proven a multiple of the vector), so the access is
 // unconditional - no branch separates the loads of an unrolled loop and they overlap.
-template <class T, int N, bool FAST = false>
+// STREAM: the run is read once and nothing near it is (a gathered table row): no L1 allocation.
+template <class T, int N, bool FAST = false, bool STREAM = false>
 __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(const T* p, int nvalid) {
   using V = typename Mem<T>::val;
   typename vec_of<V, N>::type r;
@@ -176,7 +177,10 @@ __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(
   if constexpr ((N % kPer) == 0 && (sizeof(T) == 2 || sizeof(T) == 4) && std::is_same<V, float>::value) {
     if (FAST || (nvalid >= N && (reinterpret_cast<uintptr_t>(p) & 15u) == 0)) {
 #pragma unroll
-      for (int c = 0; c < N / kPer; ++c) unpack<T>(ldg_keep(p + c * kPer), &r.v[c * kPer]);  // may be re-read: keep in L1
+      for (int c = 0; c < N / kPer; ++c) {
+        if constexpr (STREAM) unpack<T>(ldg_stream(p + c * kPer), &r.v[c * kPer]);
+        else unpack<T>(ldg_keep(p + c * kPer), &r.v[c * kPer]);  // may be re-read: keep in L1
+      }
       return r;
     }
   }
@@ -218,7 +222,7 @@ template <class T, int N, bool FAST, class I, class M, class... U>
 __device__ __forceinline__ auto igather(const T* p, const I& idx, const M& mask, typename Mem<T>::val other,
                                         int nvalid, const U&... indirect) {
   if constexpr (((rank<U>::n == 0) && ...) && rank<I>::n == N) {
-    return ldvec<T, N, FAST>(p + at(idx, 0), nvalid);
+    return ldvec<T, N, FAST, true>(p + at(idx, 0), nvalid);
   } else {
     return gather(p, idx, mask, other);
   }
@@ -1031,8 +1035,8 @@ template <class K> inline int row_resident(K kern, int threads, size_t smem = 0)
   const int slot = dev & 63;
   int n = cache[slot].load(std::memory_order_acquire);
   if (n == 0) {
-    // more than 48 KiB of dynamic shared memory needs the opt-in, once per device
-    if (smem > 48 * 1024 &&
+    // static + dynamic shared memory beyond 48 KiB needs the opt-in, once per device
+    if (smem > 32 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -1;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) return -1;
@@ -1059,10 +1063,17 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
   // happens before the launch ahead of us has completed
   pdl_launch_dependents();
   pdl_wait();
+  const long long stride = (long long)gridDim.x * TEAMS;
+  // the first row's vectors are requested before the per-column operands are loaded and
+  // widened, so that both latencies overlap (it matters for kernels of a few microseconds)
+  typename Body::Raw nxt;
+  if constexpr (TEAM >= 32 && STAGED) {
+    const long long r0 = (long long)blockIdx.x * TEAMS + c.team;
+    if (r0 < rows) body.fetch(c, r0, nxt);
+  }
   typename Body::Consts k;
   body.init(c, k);
   if constexpr (Body::kSmemConsts > 0) __syncthreads();   // the operand table is complete
-  const long long stride = (long long)gridDim.x * TEAMS;
   if constexpr (TEAM < 32) {
     // The teams of a warp run the same number of rows (full-mask shuffles inside).  Rows this
     // short give a thread one vector each, so kBatch rows are fetched before the first is
@@ -1089,10 +1100,6 @@ __global__ void __launch_bounds__(TEAM* TEAMS, MIN_CTAS)
     return;
   } else {
     long long r = (long long)blockIdx.x * TEAMS + c.team;
-    typename Body::Raw nxt;
-    if constexpr (STAGED) {
-      if (r < rows) body.fetch(c, r, nxt);
-    }
     while (r < rows) {
       const typename Body::Raw cur = nxt;
       const long long rn = r + stride;
@@ -1391,7 +1398,15 @@ int launch_outer_gen(const Body& body, long long xnumel, void* stream, bool alig
   static const long long cap_u = resident_ctas(outer_gen_kernel<Body, TX, TY, false>, TX * TY);
   const long long per_cta = (long long)TX * Body::kVec;
   long long grid = (xnumel + per_cta - 1) / per_cta;
-  const long long cap = aligned ? cap_a : cap_u;
+  // A tile ends with a CTA-wide fold during which the CTA has no loads in flight, so the grid
+  // holds several waves of CTAs (the hardware starts the next CTA's loads while another folds)
+  // instead of exactly the resident set.  IXB_OUTER_WAVES overrides the default.
+  static const long long waves = [] {
+    const char* v = getenv("IXB_OUTER_WAVES");
+    const long long w = v != nullptr ? atoll(v) : 2;
+    return w < 1 ? 1 : w;
+  }();
+  const long long cap = (aligned ? cap_a : cap_u) * waves;
   if (grid > cap) grid = cap;
   if (aligned) outer_gen_kernel<Body, TX, TY, true><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
   else outer_gen_kernel<Body, TX, TY, false><<<(unsigned)grid, TX * TY, 0, (cudaStream_t)stream>>>(body, xnumel);
