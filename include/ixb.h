@@ -231,6 +231,22 @@ int ixb_fa_fwd(int dtype, const void* q, const void* k, const void* v, void* o, 
                const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                float scale, int causal, int32_t* status, ixb_stream stream);
 
+/* Gradients of ixb_fa_fwd: dq[B,H,Sq,D], dk/dv[B,H,Sk,D] from q, k, v, the forward's
+ * output `o` and log-sum-exp `lse` [B,H,Sq] (fp32, contiguous) and the incoming gradient
+ * `dout` [B,H,Sq,D]; same dtype, stride and alignment rules as ixb_fa_fwd for all eight
+ * tensors, same meaning of `scale`, `causal` and `status`.  `delta` is caller-provided
+ * scratch of B*H*Sq floats (it receives rowsum(dout * o)); nothing is allocated and no
+ * atomics are used, so the result is deterministic.  Stands in for the vendor call
+ * torch_npu.npu_fusion_attention_grad behind npu_graph::npu_fa_backward
+ * (inductor_x/npu_fusion_attention_graph.py:38-42). */
+int ixb_fa_bwd(int dtype, const void* q, const void* k, const void* v, const void* o,
+               const void* dout, const float* lse, void* dq, void* dk, void* dv, float* delta,
+               int32_t B, int32_t H, int32_t Sq, int32_t Sk, int32_t D, const int64_t* q_strides,
+               const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+               const int64_t* do_strides, const int64_t* dq_strides, const int64_t* dk_strides,
+               const int64_t* dv_strides, float scale, int causal, int32_t* status,
+               ixb_stream stream);
+
 /* ---- context-parallel attention merge ---------------------------------------------------- */
 
 /* Fold the partial attention result of one ring step into the running one, (max, sum) form:

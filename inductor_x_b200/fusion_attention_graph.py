@@ -50,6 +50,8 @@ b200_def.define(
     "bool gen_mask_parallel=True, bool sync=False) -> (Tensor, Tensor, Tensor, Tensor)")
 # compact form used by the SDPA retargeting pass: (out, logsumexp)
 b200_def.define("b200_sdpa(Tensor query, Tensor key, Tensor value, float scale, bool is_causal) -> (Tensor, Tensor)")
+b200_def.define("b200_sdpa_backward(Tensor query, Tensor key, Tensor value, Tensor out, Tensor lse, Tensor dout, "
+                "float scale, bool is_causal) -> (Tensor, Tensor, Tensor)")
 
 b200_cuda = Library(NAMESPACE, "IMPL", "CUDA")
 b200_meta = Library(NAMESPACE, "IMPL", "Meta")
@@ -150,22 +152,33 @@ def b200_fa_meta(query, key, value, head_num, input_layout, pse=None, padding_ma
             torch.empty([1], dtype=torch.int64, device="meta"))
 
 
+def _run_backward_kernel(q, k, v, out, lse, dout, scale: float, causal: bool):
+    """(dq, dk, dv) in the dtype of q from the tcgen05 backward kernels (BNSD views)."""
+    from . import config, ops
+
+    dt = q.dtype
+    if dt == torch.float32:
+        if not config.attention_fp32_as_fp16:
+            raise TypeError("b200_fa_backward: float32 operands would be narrowed to float16 for the "
+                            "tensor-core kernel; set IXB_ATTENTION_FP32_AS_FP16=1 to allow it")
+        q, k, v, out, dout = (t.to(torch.float16) for t in (q, k, v, out, dout))
+    fix = lambda t: t if t.stride(-1) == 1 and all(st % 8 == 0 for st in t.stride()[:3]) else t.contiguous()
+    dq, dk, dv = ops.fused_attention_backward(fix(q), fix(k), fix(v), fix(out), lse, fix(dout), scale,
+                                              causal=causal)
+    return dq.to(dt), dk.to(dt), dv.to(dt)
+
+
 def b200_fa_backward_impl(query, key, value, dy, head_num, input_layout, *, pse=None, padding_mask=None,
                           atten_mask=None, softmax_max=None, softmax_sum=None, softmax_in=None,
                           attention_in=None, scale_value=1.0, keep_prob=1.0, pre_tockens=TOKEN_MAX,
                           next_tockens=TOKEN_MAX, inner_precise=0, seed=None, offset=None, numels=None,
                           prefix=None, actual_seq_qlen=None, actual_seq_kvlen=None, sparse_mode=0,
                           gen_mask_parallel=True, sync=False):
-    """Gradients of the fused attention from the saved log-sum-exp, recomputing the
-    probabilities block of heads by block of heads:
-
-        P = exp(Q K^T * m - lse);  dV = P^T dO;  dP = dO V^T
-        dS = P * (dP - rowsum(P * dP)) * m;  dQ = dS K;  dK = dS^T Q
-
-    This is NOT a hand-written kernel: the five products are library GEMMs (fp32) and the
-    element-wise steps are torch ops on the device.  It makes the op pair and the autograd
-    wrapper of the reference's surface (``npu_fusion_attention_graph.py:38-42,114-123``)
-    work end to end; a tcgen05 backward kernel is what would replace it."""
+    """Gradients of the fused attention from the statistics the forward saved
+    (``npu_fusion_attention_graph.py:38-42``).  The log-sum-exp is rebuilt from the
+    ``(softmax_max, softmax_sum)`` pair, the probabilities are recomputed tile by tile inside
+    the tcgen05 kernels behind ``ixb_fa_bwd``; as in the forward op, ``scale_value`` carries
+    ``inv_scale_factor``."""
     if pse is not None or padding_mask is not None or keep_prob != 1.0:
         raise NotImplementedError("b200_fa_backward: pse, padding_mask and dropout are not supported")
     if softmax_max is None or softmax_sum is None or attention_in is None:
@@ -176,36 +189,13 @@ def b200_fa_backward_impl(query, key, value, dy, head_num, input_layout, *, pse=
     q = _to_bnsd(query, input_layout, head_num)
     k = _to_bnsd(key, input_layout, head_num)
     v = _to_bnsd(value, input_layout, head_num)
-    do = _to_bnsd(dy.contiguous(), input_layout, head_num)
-    B, N, Sq, D = q.shape
-    Sk = k.shape[2]
-    mult = 1.0 / scale_value
+    o = _to_bnsd(attention_in, input_layout, head_num)
+    do = _to_bnsd(dy, input_layout, head_num)
+    if sparse_mode == 2 and q.shape[2] != k.shape[2]:
+        raise NotImplementedError("b200_fa_backward: left-up causal needs equal sequence lengths")
     lse = softmax_max[..., 0] + torch.log(softmax_sum[..., 0])           # [B, N, Sq]
-    dq = torch.empty((B, N, Sq, D), dtype=torch.float32, device=q.device)
-    dk = torch.empty((B, N, Sk, D), dtype=torch.float32, device=q.device)
-    dv = torch.empty((B, N, Sk, D), dtype=torch.float32, device=q.device)
-    keep = None
-    if causal:
-        i = torch.arange(Sq, device=q.device).unsqueeze(1)
-        j = torch.arange(Sk, device=q.device).unsqueeze(0)
-        keep = j <= i + (Sk - Sq)
-    # heads per block: keep the fp32 score block under about 256 MiB
-    per = max(1, min(N, (64 << 20) // max(1, Sq * Sk)))
-    for b in range(B):
-        for n0 in range(0, N, per):
-            sl = (b, slice(n0, n0 + per))
-            qf, kf, vf, dof = q[sl].float(), k[sl].float(), v[sl].float(), do[sl].float()
-            p = torch.matmul(qf, kf.transpose(-1, -2)).mul_(mult).sub_(lse[sl].unsqueeze(-1)).exp_()
-            if keep is not None:
-                p = p * keep
-            dv[sl] = torch.matmul(p.transpose(-1, -2), dof)
-            dp = torch.matmul(dof, vf.transpose(-1, -2))
-            # rowsum(P * dP) is rowsum(dO * O) with the exact O, not the 16-bit one that was stored
-            ds = dp.sub_((p * dp).sum(-1, keepdim=True)).mul_(p).mul_(mult)
-            dq[sl] = torch.matmul(ds, kf)
-            dk[sl] = torch.matmul(ds.transpose(-1, -2), qf)
-    cast = lambda t, like: _from_bnsd(t.to(like.dtype), input_layout)
-    return cast(dq, query), cast(dk, key), cast(dv, value), None
+    dq, dk, dv = _run_backward_kernel(q, k, v, o, lse, do, 1.0 / scale_value, causal)
+    return (_from_bnsd(dq, input_layout), _from_bnsd(dk, input_layout), _from_bnsd(dv, input_layout), None)
 
 
 def b200_fa_backward_meta(query, key, value, dy, head_num, input_layout, **kwargs):
@@ -229,13 +219,43 @@ b200_cuda.impl("b200_fa", b200_fa_impl)
 b200_meta.impl("b200_fa", b200_fa_meta)
 b200_cuda.impl("b200_fa_backward", b200_fa_backward_impl)
 b200_meta.impl("b200_fa_backward", b200_fa_backward_meta)
+def b200_sdpa_backward_impl(query, key, value, out, lse, dout, scale, is_causal):
+    return _run_backward_kernel(query, key, value, out, lse, dout, scale, is_causal)
+
+
+def b200_sdpa_backward_meta(query, key, value, out, lse, dout, scale, is_causal):
+    new = lambda t: torch.empty(t.shape, dtype=t.dtype, device="meta")
+    return new(query), new(key), new(value)
+
+
 b200_cuda.impl("b200_sdpa", b200_sdpa_impl)
 b200_meta.impl("b200_sdpa", b200_sdpa_meta)
+b200_cuda.impl("b200_sdpa_backward", b200_sdpa_backward_impl)
+b200_meta.impl("b200_sdpa_backward", b200_sdpa_backward_meta)
+
+
+def _sdpa_setup_context(ctx, inputs, output):
+    query, key, value, scale, is_causal = inputs
+    out, lse = output
+    ctx.save_for_backward(query, key, value, out, lse)
+    ctx.scale, ctx.is_causal = scale, is_causal
+
+
+def _sdpa_backward(ctx, d_out, d_lse):
+    query, key, value, out, lse = ctx.saved_tensors
+    dq, dk, dv = torch.ops.b200_graph.b200_sdpa_backward(query, key, value, out, lse, d_out, ctx.scale,
+                                                         ctx.is_causal)
+    return dq, dk, dv, None, None
+
+
+# gradients of the compact op (the log-sum-exp output is not differentiated through)
+torch.library.register_autograd("b200_graph::b200_sdpa", _sdpa_backward, setup_context=_sdpa_setup_context,
+                                lib=b200_def)
 
 
 class B200GraphAttentionFunction(Function):
     """Autograd wrapper (``NpuGraphAttentionFunction``, ``:88-123``): forward on the tcgen05
-    kernel, backward through ``b200_fa_backward`` (library GEMMs, see there)."""
+    kernel, backward through ``b200_fa_backward`` (the tcgen05 backward kernels)."""
 
     @staticmethod
     def forward(ctx, query, key, value, head_num, input_layout, pse=None, padding_mask=None,
@@ -420,6 +440,27 @@ def _pattern_extra_check(match) -> bool:
     return meta.dtype in (torch.float16, torch.bfloat16)
 
 
+def _joint_fwd_bwd_folded(fn, args):
+    """``joint_fwd_bwd`` with the 0-d ``scalar_tensor`` nodes of the trace (the zero that the
+    gradient of ``where`` fills in) rewritten to ``full([], value)``: Inductor's constant
+    folding has done that to the joint graph by the time the patterns are matched."""
+    from torch._inductor.pattern_matcher import joint_fwd_bwd
+
+    gm = joint_fwd_bwd(fn, args)
+    for node in list(gm.graph.nodes):
+        if node.op == "call_function" and node.target is aten.scalar_tensor.default:
+            with gm.graph.inserting_before(node):
+                full = gm.graph.call_function(
+                    aten.full.default, ([], node.args[0]),
+                    {"dtype": node.kwargs.get("dtype"), "device": node.kwargs.get("device"), "pin_memory": False})
+            full.meta.update(node.meta)
+            node.replace_all_uses_with(full)
+            gm.graph.erase_node(node)
+    gm.graph.lint()
+    gm.recompile()
+    return gm
+
+
 def _get_sfdp_patterns():
     from torch._inductor.fx_passes.fuse_attention import partialize_and_update_signature
     from torch._inductor.fx_passes.joint_graph import patterns
@@ -437,10 +478,17 @@ def _get_sfdp_patterns():
         pattern, replacement = _b200_fusion_attention_graph_pattern_1, _b200_fusion_attention_graph_replacement_1
         args = [g(), g(), g(), c()]
         name = f"{pattern.__name__}_{dtype}"
-        # the training (joint) variant is registered only when a backward kernel exists;
         # the inference variant drops dropout, exactly as the reference partialises it
+        # (:206-216).  The reference's training variant keeps dropout (:196-204), which these
+        # kernels do not have (keep_prob != 1 raises); the training variant registered here is
+        # the dropout-free form, gradients through b200_fa_backward
         pattern_i = partialize_and_update_signature(pattern, dropout_p=0.0)
         replacement_i = partialize_and_update_signature(replacement, dropout_p=0.0)
+        yield name + "_training", {
+            "search_fn": pattern_i, "replace_fn": replacement_i, "example_inputs": args,
+            "trace_fn": joint_fwd_bwd, "pass_dicts": patterns, "scalar_workaround": {},
+            "extra_check": _pattern_extra_check,
+        }
         yield name + "_inference", {
             "search_fn": pattern_i, "replace_fn": replacement_i, "example_inputs": args,
             "trace_fn": fwd_only, "pass_dicts": patterns, "scalar_workaround": {},
@@ -450,10 +498,19 @@ def _get_sfdp_patterns():
     # the fp16 opt-in): half types trace differently (casts around the softmax)
     for dtype in [torch.bfloat16, torch.float16, torch.float]:
         b_inp = functools.partial(torch.empty, (2, 4, 8, 128), device=device, dtype=dtype)
+        t_inp = functools.partial(b_inp, requires_grad=True)
         keep = functools.partial(torch.ones, (8, 8), device=device, dtype=torch.bool)
         c = functools.partial(c_inp, dtype=dtype)      # same dtype: no cast node around the scalar
         for pattern, replacement in ((_b200_causal_attention_pattern_mul, _b200_causal_attention_replacement_mul),
                                      (_b200_causal_attention_pattern_div, _b200_causal_attention_replacement_div)):
+            # training: forward and backward of the pattern are matched in the joint graph and
+            # replaced by b200_sdpa and its registered gradient (b200_sdpa_backward)
+            yield f"{pattern.__name__}_{dtype}_training", {
+                "search_fn": pattern, "replace_fn": replacement,
+                "example_inputs": [t_inp(), t_inp(), t_inp(), keep(), c()],
+                "trace_fn": _joint_fwd_bwd_folded, "pass_dicts": patterns, "scalar_workaround": {},
+                "extra_check": _causal_extra_check,
+            }
             yield f"{pattern.__name__}_{dtype}_inference", {
                 "search_fn": pattern, "replace_fn": replacement,
                 "example_inputs": [b_inp(), b_inp(), b_inp(), keep(), c()],

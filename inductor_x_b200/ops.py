@@ -226,6 +226,45 @@ def fused_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
     return (out, lse) if return_lse else out
 
 
+def fused_attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                             lse: torch.Tensor, dout: torch.Tensor, scale: float, *, causal: bool = False,
+                             check: bool = False):
+    """Gradients ``(dq, dk, dv)`` of :func:`fused_attention` from its inputs, its output
+    ``out``, its log-sum-exp ``lse`` (``return_lse=True``) and the incoming gradient ``dout``
+    (tcgen05 kernels behind ``ixb_fa_bwd``; deterministic, no atomics)."""
+    _need_cuda(q, k, v, out, dout, lse)
+    if q.dim() != 4 or k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
+        raise ValueError("expected q[B,H,Sq,D], k[B,H,Sk,D], v[B,H,Sk,D]")
+    if out.shape != q.shape or dout.shape != q.shape:
+        raise ValueError("out and dout must have the shape of q")
+    if q.dtype not in (torch.float16, torch.bfloat16) or any(t.dtype != q.dtype for t in (k, v, out, dout)):
+        raise ValueError("q, k, v, out, dout must share dtype float16 or bfloat16")
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if lse.shape != (B, H, Sq) or lse.dtype != torch.float32:
+        raise ValueError("lse must be float32 [B, H, Sq]")
+    lse = lse.contiguous()
+    if dout.stride(3) != 1 or any(st % 8 for st in dout.stride()[:3]):
+        dout = dout.contiguous()
+    for t in (q, k, v, out, dout):
+        if t.stride(3) != 1:
+            raise ValueError("the head dimension must be contiguous")
+    dq = torch.empty((B, H, Sq, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, H, Sk, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, H, Sk, D), dtype=q.dtype, device=q.device)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
+    rt.check("ixb_fa_bwd", rt.load().ixb_fa_bwd(
+        rt.DTYPE_CODE[q.dtype], q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+        lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), B, H, Sq, Sk, D,
+        _bhs_strides(q), _bhs_strides(k), _bhs_strides(v), _bhs_strides(out), _bhs_strides(dout),
+        _bhs_strides(dq), _bhs_strides(dk), _bhs_strides(dv), float(scale), int(causal), rt.ptr(status),
+        rt.raw_stream(q.device)))
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError("ixb_fa_bwd: an internal pipeline wait gave up; gradients are undefined")
+    return dq, dk, dv
+
+
 # ---- context-parallel attention merge ----------------------------------------------------
 def _stat_nstride(t: torch.Tensor, S: int) -> int:
     """Element stride of the N axis of a ``[B, N, S, 8]`` statistics tensor whose last two

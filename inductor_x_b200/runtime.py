@@ -103,6 +103,8 @@ _SIGNATURES = {
     "ixb_fa_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                            c_int32, c_int32, c_int32, POINTER(c_int64), POINTER(c_int64),
                            POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_void_p, c_void_p]),
+    "ixb_fa_bwd": (c_int, [c_int] + [c_void_p] * 10 + [c_int32] * 5 + [POINTER(c_int64)] * 8 +
+                   [c_float, c_int, c_void_p, c_void_p]),
     "ixb_index_select_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                       c_int, c_int, c_void_p, c_void_p]),
     "ixb_cp_forward_update": (c_int, [c_int] + [c_void_p] * 9 + [c_int32] * 4 + [c_int64] * 3 + [c_void_p]),

@@ -90,6 +90,27 @@ def attention(q, k, v, scale, causal=True, compute=torch.float32):
     return out, lse
 
 
+def attention_backward(q, k, v, dout, scale, causal=True):
+    """(dq, dk, dv) of `attention` by autograd through its fp32 eager form, one (batch, head)
+    at a time.  The reference delegates these gradients to the vendor call
+    torch_npu.npu_fusion_attention_grad (``inductor_x/npu_fusion_attention_graph.py:38-42``),
+    which is not in its tree: this restates the published math, parity unpinned."""
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    dq, dk, dv = torch.empty_like(q, dtype=torch.float32), torch.empty_like(k, dtype=torch.float32), \
+        torch.empty_like(v, dtype=torch.float32)
+    mask = torch.ones(Sq, Sk, dtype=torch.bool).tril(diagonal=Sk - Sq) if causal else None
+    for b in range(B):
+        for h in range(H):
+            qf, kf, vf = (t[b, h].float().clone().requires_grad_(True) for t in (q, k, v))
+            s = (qf @ kf.t()) * scale
+            if mask is not None:
+                s = s.masked_fill(~mask, float("-inf"))
+            (torch.softmax(s, dim=-1) @ vf).backward(dout[b, h].float())
+            dq[b, h], dk[b, h], dv[b, h] = qf.grad, kf.grad, vf.grad
+    return dq, dk, dv
+
+
 # ----------------------------------------------------------------------------- config 5
 def rmsnorm(x, w, eps=1e-6, compute=torch.float32):
     xf = x.to(compute)

@@ -113,3 +113,55 @@ def test_lower_triangular_proof():
     assert not _is_lower_triangular(last(lambda: torch.ones(8, 8, dtype=torch.bool).tril(1)))
     assert not _is_lower_triangular(last(lambda: torch.ones(8, 8, dtype=torch.bool).tril(-1)))
     assert not _is_lower_triangular(last(lambda: torch.rand(8, 8) > 0.5))
+
+
+def _joint_targets(fn, *args):
+    """Call targets of the joint (forward + backward) graph after the joint-graph patterns."""
+    import inductor_x_b200  # noqa: F401
+
+    seen = {}
+
+    def grab(graph):
+        seen["targets"] = [str(n.target) for n in graph.nodes if n.op == "call_function"]
+        raise _Stop()
+
+    old = (torch._inductor.config.joint_custom_post_pass, torch._inductor.config.fx_graph_cache)
+    torch._inductor.config.joint_custom_post_pass = grab
+    torch._inductor.config.fx_graph_cache = False
+    torch._dynamo.reset()
+    try:
+        torch.compile(fn)(*args)
+    except Exception:
+        pass
+    finally:
+        torch._inductor.config.joint_custom_post_pass, torch._inductor.config.fx_graph_cache = old
+        torch._dynamo.reset()
+    return seen.get("targets", [])
+
+
+@pytest.mark.parametrize("form", ["mul", "div"])
+def test_training_graph_of_literal_causal_attention_is_matched(form):
+    """With gradients required, forward AND backward of the pattern are replaced in the joint
+    graph: the compact op and its registered gradient, no batched matmul left."""
+    q, k, v = (torch.randn(2, 4, 64, 128).bfloat16().requires_grad_() for _ in range(3))
+    targets = _joint_targets(_literal_attention("tril", form, 1 / math.sqrt(128)), q, k, v)
+    assert "b200_graph.b200_sdpa.default" in targets
+    assert "b200_graph.b200_sdpa_backward.default" in targets
+    assert "aten.bmm.default" not in targets
+    # an upper-triangular mask is left alone in training as well
+    targets = _joint_targets(_literal_attention("triu", form, 0.1), q, k, v)
+    assert "b200_graph.b200_sdpa.default" not in targets and targets.count("aten.bmm.default") == 6
+
+
+def test_training_graph_of_the_reference_pattern_is_matched():
+    """The reference's pattern 1 without dropout (permute x3, matmul, div, softmax, matmul)
+    in a training graph: b200_fa forward, b200_fa_backward for the gradients."""
+    def attention(q, k, v):
+        q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        return torch.matmul(q, k.transpose(-2, -1)).div(11.3).softmax(dim=-1).matmul(v)
+
+    q, k, v = (torch.randn(2, 64, 4, 128).half().requires_grad_() for _ in range(3))
+    targets = _joint_targets(attention, q, k, v)
+    assert "b200_graph.b200_fa.default" in targets
+    assert "b200_graph.b200_fa_backward.default" in targets
+    assert "aten.bmm.default" not in targets
