@@ -479,6 +479,68 @@ class FusedAttention(Workload):
         return fn, 4 * heads * self.S * self.S * self.D // 2, f"{heads} of {self.B * self.H} heads, CPU SDPA fp32"
 
 
+class FusedAttentionTraining(FusedAttention):
+    """Training step of configs[3]: forward and backward of the same literal causal graph with
+    gradients required.  The joint-graph pattern replaces both halves: the forward kernel, then
+    delta, dK/dV and dQ kernels (tcgen05).  FLOPs: 3.5 x the forward count (2 forward products
+    + 5 backward products, causal halves) - the recomputed probabilities of the two backward
+    kernels (7 products actually issued) are not counted."""
+
+    name = "fused_attention_fwd_bwd_bf16_b8_h32_s4096_d128_causal"
+    metric = "fused-attention training TFLOP/s (forward + backward)"
+    graph_capture = False     # autograd runs the backward graph: timed as an enqueue loop
+
+    def flops(self):
+        return 7 * super().flops() // 2
+
+    def algorithmic_bytes(self):
+        return 8 * self.B * self.H * self.S * self.D * 2
+
+    def setup(self, device, seed, n_sets=1):
+        super().setup(device, seed, n_sets)
+        for t in (self.q, self.k, self.v):
+            t.requires_grad_(True)
+        g = torch.Generator().manual_seed(100 + seed)
+        self.dy = torch.randn(self.q.shape, generator=g).to(self.q.dtype).to(device)
+
+    def op(self, q, k, v):
+        out = self.compiled(q, k, v) if self.path == "compiled" else self.prebuilt(q, k, v)
+        return (out,) + torch.autograd.grad(out, (q, k, v), self.dy)
+
+    def prebuilt(self, q, k, v):
+        from inductor_x_b200.fusion_attention_graph import b200_fusion_attention_graph
+
+        return b200_fusion_attention_graph(q, k, v, self.H, "BNSD", scale=1.0 / self.scale, sparse_mode=3)[0]
+
+    def e2e_setup(self, device):
+        self.h = [self.host[n].pin_memory() for n in "qkv"]
+        self.h_dy = self.dy.cpu().pin_memory()
+        self.d = [torch.empty_like(self.q).requires_grad_(True) for _ in range(3)]
+        self.h_g = [torch.empty_like(self.h[0]).pin_memory() for _ in range(3)]
+
+    def e2e_step(self):
+        with torch.no_grad():
+            for dst, src in zip(self.d, self.h):
+                dst.copy_(src, non_blocking=True)
+            self.dy.copy_(self.h_dy, non_blocking=True)
+        res = self.op(*self.d)
+        for dst, src in zip(self.h_g, res[1:]):
+            dst.copy_(src, non_blocking=True)
+        return 4 * self.h[0].numel() * 2, 3 * self.h[0].numel() * 2
+
+    def cpu_sample(self, heads=1):
+        q, k, v = (self.host[n][:1, :heads].float().requires_grad_(True) for n in "qkv")
+        dy = torch.ones_like(q)
+        keep = torch.ones(self.S, self.S, dtype=torch.bool).tril()
+
+        def fn():
+            s = (q @ k.transpose(-1, -2) * self.scale).masked_fill(~keep, float("-inf"))
+            return torch.autograd.grad(torch.softmax(s, -1) @ v, (q, k, v), dy)
+
+        return fn, 7 * (4 * heads * self.S * self.S * self.D // 2) // 2, \
+            f"{heads} of {self.B * self.H} heads, eager fp32 attention + autograd on CPU"
+
+
 class LlamaLayer(Workload):
     """configs[4]: Llama-style decoder layer through torch.compile (this backend): hidden 4096,
     32 heads x 128, SwiGLU 11008, batch 16 x seq 2048, bf16.  GEMMs stay extern (cuBLAS) as in
@@ -677,11 +739,11 @@ class TransposedPointwise(PermutedPointwise):
 
 WORKLOADS = {
     "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
-    "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention,
+    "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention, "c4_train": FusedAttentionTraining,
     "c5": LlamaLayer, "cp": CpMerge, "perm": PermutedPointwise, "transpose": TransposedPointwise,
 }
 #: configurations reported under `configs` after the headline: (key, steps per replay, replays floor)
-SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "perm", "transpose", "c4", "c5")
+SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "perm", "transpose", "c4", "c4_train", "c5")
 
 
 # ---------------------------------------------------------------------------- driver
@@ -1071,7 +1133,7 @@ def main():
         if env.world == 1:
             for key in SECONDARY:
                 try:
-                    steps = {"c4": 4, "c5": 3}.get(key, 40)
+                    steps = {"c4": 4, "c4_train": 2, "c5": 3}.get(key, 40)
                     configs.append(run_config(env, key, args,
                                               args.path if key not in ("c5", "perm", "transpose") else "compiled",
                                               steps=steps, min_seconds=0.3, e2e_steps=2))

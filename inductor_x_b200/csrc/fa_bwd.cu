@@ -17,10 +17,12 @@
 // The probabilities are recomputed in both kernels (7 products instead of 5) - that is what
 // keeps each output with a single owner.
 //
-// Ten warps per CTA: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 the element-wise
-// work; the two groups of four warps split the 128 columns of a tile in halves (a warp may
-// only touch the 32 TMEM lanes of its quadrant).  Every wait is bounded; a wait that gives up
-// raises a flag in `status` and lets the CTA drain and exit.
+// Eighteen warps per CTA: warp 0 TMA producer, warp 1 MMA issuer, warps 2-17 the
+// element-wise work in four groups of four warps that split the 128 columns of a tile in
+// quarters (a warp may only touch the 32 TMEM lanes of its quadrant; no row reduction is
+// needed here, so the split costs nothing and four warps per scheduler hide the TMEM,
+// shared-memory and ex2 latencies that two cannot).  Every wait is bounded; a wait that gives
+// up raises a flag in `status` and lets the CTA drain and exit.
 #include <atomic>
 #include "fa_maps.h"
 #include "ixb/tcgen05.cuh"
@@ -35,7 +37,10 @@ constexpr int HD = 128;  // head dimension
 constexpr int kStages = 2;
 constexpr int kTileBytes = 128 * HD * 2;
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kThreads = 64 + 256;
+constexpr int NG = 4;             // groups of element-wise warps; each takes 128 / NG columns of a tile
+constexpr int GC = 128 / NG;      // columns per group
+constexpr int kWorkers = 128 * NG;
+constexpr int kThreads = 64 + kWorkers;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
 constexpr size_t kSmemBytes = (size_t)kTileBytes * 6 + 1024;
@@ -74,20 +79,26 @@ __global__ void __launch_bounds__(256)
     fa_bwd_delta_kernel(const unsigned char* o, const unsigned char* dout, float* delta, int H, int Sq,
                         long long rows, long long o_sb, long long o_sh, long long o_ss, long long d_sb,
                         long long d_sh, long long d_ss) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const long long bh = row / Sq;
-  const long long i = row - bh * Sq;
-  const long long b = bh / H, h = bh - b * H;
-  const uint2 a = *reinterpret_cast<const uint2*>(o + 2 * (b * o_sb + h * o_sh + i * o_ss) + lane * 8);
-  const uint2 g = *reinterpret_cast<const uint2*>(dout + 2 * (b * d_sb + h * d_sh + i * d_ss) + lane * 8);
-  const float2 a0 = unpack_pair(a.x, IS_BF16), a1 = unpack_pair(a.y, IS_BF16);
-  const float2 g0 = unpack_pair(g.x, IS_BF16), g1 = unpack_pair(g.y, IS_BF16);
-  float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  // half a warp per row: 16 lanes x 16 bytes = the 128 16-bit values of a row
+  const int lane = threadIdx.x & 31, sub = lane & 15;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+  float s = 0.f;
+  if (row < rows) {
+    const long long bh = row / Sq;
+    const long long i = row - bh * Sq;
+    const long long b = bh / H, h = bh - b * H;
+    const uint4 a = ldg_stream(reinterpret_cast<const uint4*>(o + 2 * (b * o_sb + h * o_sh + i * o_ss) + sub * 16));
+    const uint4 g = ldg_stream(reinterpret_cast<const uint4*>(dout + 2 * (b * d_sb + h * d_sh + i * d_ss) + sub * 16));
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
-  if (lane == 0) delta[row] = s;
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = unpack_pair(aw[e], IS_BF16), y = unpack_pair(gw[e], IS_BF16);
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(kFull, s, off);
+  if (sub == 0 && row < rows) delta[row] = s;
 }
 
 // --------------------------------------------------------------------- shared pieces
@@ -117,22 +128,24 @@ __device__ __forceinline__ void issue_ss(uint32_t d, uint64_t a_desc, uint64_t b
     tc::mma_ss(d, a_desc + off, b_desc + off, idesc, ks > 0);
   }
 }
-// D (+)= A B with A in TMEM as 16-bit pairs (the halves [0,64) and [64,128) of the reduced
-// index sit at columns a and a + 64) and B a tile in MN-major form (16 rows = 2048 bytes a step)
+// D (+)= A B with A in TMEM as 16-bit pairs (group g wrote its GC values of the reduced index
+// as GC / 2 columns starting at column a + GC * g) and B a tile in MN-major form (16 rows =
+// 2048 bytes a step)
 __device__ __forceinline__ void issue_ts(uint32_t d, uint32_t a, uint64_t b_desc_mn, uint32_t idesc,
                                          bool accumulate) {
 #pragma unroll
   for (int ks = 0; ks < 128 / 16; ++ks) {
-    const uint32_t col = a + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+    constexpr int kStepsPerGroup = GC / 16;
+    const uint32_t col = a + (ks / kStepsPerGroup) * GC + (ks % kStepsPerGroup) * 8;
     tc::mma_ts(d, col, b_desc_mn + (uint32_t)(ks * 2048 >> 4), idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
-// 64 accumulator columns of this thread's row -> 16-bit row in global memory (128 bytes)
+// GC accumulator columns of this thread's row -> 16-bit values in global memory
 template <bool IS_BF16>
-__device__ __forceinline__ void store_half_row(uint32_t taddr, unsigned char* dst, float mult, bool live) {
+__device__ __forceinline__ void store_cols(uint32_t taddr, unsigned char* dst, float mult, bool live) {
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < GC / 32; ++c) {
     uint32_t acc[32];
     tc::tmem_ld32(taddr + c * 32, acc);
     tc::tmem_wait_ld();
@@ -196,8 +209,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&p_full, 256);
-    mbar_init(&ds_full, 256);
+    mbar_init(&p_full, kWorkers);
+    mbar_init(&ds_full, kWorkers);
     mbar_init(&acc_done, 1);
     failed = 0;
     mbar_init_fence();
@@ -303,13 +316,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ element-wise work
-    const int g = (warp - 2) >> 2;  // half of the query columns
+    const int g = (warp - 2) >> 2;  // group: query columns [GC g, GC g + GC) of a tile
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // key inside the tile
     const int kj = kt0 + row;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t s_addr = lane_addr + kColS + 64 * g;
-    const uint32_t dp_addr = lane_addr + kColDP + 64 * g;
+    const uint32_t s_addr = lane_addr + kColS + GC * g;
+    const uint32_t dp_addr = lane_addr + kColDP + GC * g;
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
 
@@ -323,34 +336,38 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc::fence_after_sync();
-      uint32_t raw[64];
-      tc::tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-      tc::tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
-      tc::tmem_wait_ld();
-      // query column e of this half is visible to key kj when qt0 + 64 g + e >= kj - diag
+      // query column e of this group is visible to key kj when qt0 + GC g + e >= kj - diag
       const bool edge = p.causal && (kt0 + BN - 1 > qt0 + diag);
-      const int lo = edge ? kj - diag - (qt0 + 64 * g) : 0;
-      const float* lse_row = &lse_s[s][64 * g];
-      float pr[64];
+      const int lo = edge ? kj - diag - (qt0 + GC * g) : 0;
+      const float* lse_row = &lse_s[s][GC * g];
+      float pr[GC];
 #pragma unroll
-      for (int e = 0; e < 64; e += 4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(lse_row + e);
-        const float2 a0 = fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2,
-                               make_float2(-l4.x, -l4.y));
-        const float2 a1 = fma2(make_float2(__uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3])), sc2,
-                               make_float2(-l4.z, -l4.w));
-        pr[e] = fast_exp2(a0.x);
-        pr[e + 1] = fast_exp2(a0.y);
-        pr[e + 2] = fast_exp2(a1.x);
-        pr[e + 3] = fast_exp2(a1.y);
-        if (edge) {
+      for (int c = 0; c < GC / 32; ++c) {
+        uint32_t raw[32];
+        tc::tmem_ld32(s_addr + c * 32, raw);
+        tc::tmem_wait_ld();
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (e + u < lo) pr[e + u] = 0.f;
+        for (int e = 0; e < 32; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse_row + c * 32 + e);
+          const float2 a0 = fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2,
+                                 make_float2(-l4.x, -l4.y));
+          const float2 a1 = fma2(make_float2(__uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3])), sc2,
+                                 make_float2(-l4.z, -l4.w));
+          float* o = &pr[c * 32 + e];
+          o[0] = fast_exp2(a0.x);
+          o[1] = fast_exp2(a0.y);
+          o[2] = fast_exp2(a1.x);
+          o[3] = fast_exp2(a1.y);
+          if (edge) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (c * 32 + e + u < lo) o[u] = 0.f;
+          }
         }
       }
+      // all of this group's S columns are in registers: P^T goes over their first half
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < GC / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack_pair(pr[c * 32 + 2 * e], pr[c * 32 + 2 * e + 1], IS_BF16);
@@ -365,9 +382,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc::fence_after_sync();
-      const float* delta_row = &delta_s[s][64 * g];
+      const float* delta_row = &delta_s[s][GC * g];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < GC / 32; ++c) {
         uint32_t d[32];
         tc::tmem_ld32(dp_addr + c * 32, d);
         tc::tmem_wait_ld();
@@ -382,7 +399,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           pk[e / 2] = pack_pair(x0, x1, IS_BF16);
           pk[e / 2 + 1] = pack_pair(x2, x3, IS_BF16);
         }
-        // columns [16c, 16c+16) of this half: their dP values are already in registers
+        // columns [16c, 16c+16) of this group: their dP values are already in registers
         tc::tmem_st16(dp_addr + c * 16, pk);
       }
       tc::tmem_wait_st();
@@ -397,18 +414,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool live = kj < p.Sk;
       unsigned char* dv_row = reinterpret_cast<unsigned char*>(p.dv.ptr) +
                               2 * ((long long)b * p.dv.sb + (long long)h * p.dv.sh + (long long)kj * p.dv.ss) +
-                              128 * g;
+                              2 * GC * g;
       unsigned char* dk_row = reinterpret_cast<unsigned char*>(p.dk.ptr) +
                               2 * ((long long)b * p.dk.sb + (long long)h * p.dk.sh + (long long)kj * p.dk.ss) +
-                              128 * g;
+                              2 * GC * g;
       if (n_it > 0) {
-        store_half_row<IS_BF16>(lane_addr + kColAcc0 + 64 * g, dv_row, 1.f, live);
-        store_half_row<IS_BF16>(lane_addr + kColAcc1 + 64 * g, dk_row, p.scale, live);
+        store_cols<IS_BF16>(lane_addr + kColAcc0 + GC * g, dv_row, 1.f, live);
+        store_cols<IS_BF16>(lane_addr + kColAcc1 + GC * g, dk_row, p.scale, live);
       } else if (live) {
         // no query sees this key tile: the gradients are zero
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < GC / 8; ++e) {
           reinterpret_cast<uint4*>(dv_row)[e] = z;
           reinterpret_cast<uint4*>(dk_row)[e] = z;
         }
@@ -428,7 +445,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ------------------------------------------------------------------------------ dQ
-// TMEM columns: [0,128) S, [128,256) dP then dS, [256,384) dQ.
+// TMEM columns: [0,128) S, [128,256) dP then dS (group g's GC values as GC / 2 columns at
+// 128 + GC g), [256,384) dQ.
 template <bool IS_BF16>
 __global__ void __launch_bounds__(kThreads, 1)
     fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -474,8 +492,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&s_read, 256);
-    mbar_init(&ds_full, 256);
+    mbar_init(&s_read, kWorkers);
+    mbar_init(&ds_full, kWorkers);
     mbar_init(&acc_done, 1);
     failed = 0;
     mbar_init_fence();
@@ -566,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ element-wise work
-    const int g = (warp - 2) >> 2;  // half of the key columns
+    const int g = (warp - 2) >> 2;  // group: key columns [GC g, GC g + GC) of a tile
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int qi = qt0 + row;
@@ -575,8 +593,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float lse2 = live ? p.lse[stat_at] * kLog2e : INFINITY;
     const float dl = live ? p.delta[stat_at] : 0.f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t s_addr = lane_addr + kColS + 64 * g;
-    const uint32_t dp_addr = lane_addr + kColDP + 64 * g;
+    const uint32_t s_addr = lane_addr + kColS + GC * g;
+    const uint32_t dp_addr = lane_addr + kColDP + GC * g;
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     const float2 nl2 = make_float2(-lse2, -lse2);
     bool ok = true;
@@ -587,23 +605,23 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc::fence_after_sync();
-      uint32_t raw[64];
-      tc::tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-      tc::tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+      uint32_t raw[GC];
+#pragma unroll
+      for (int c = 0; c < GC / 32; ++c) tc::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(&s_read);
-      const int col0 = j * BN + 64 * g;
+      const int col0 = j * BN + GC * g;
       const bool edge = (j * BN + BN > p.Sk) || (p.causal && (j * BN + BN - 1 > qt0 + diag));
-      int lim = 63;  // last visible key of this row, relative to this half of the tile
+      int lim = GC - 1;  // last visible key of this row, relative to this group's columns
       if (edge) {
         int last = p.Sk - 1;
         if (p.causal && qi + diag < last) last = qi + diag;
         lim = last - col0;
       }
-      float pr[64];
+      float pr[GC];
 #pragma unroll
-      for (int e = 0; e < 64; e += 2) {
+      for (int e = 0; e < GC; e += 2) {
         const float2 a = fma2(make_float2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1])), sc2, nl2);
         pr[e] = fast_exp2(a.x);
         pr[e + 1] = fast_exp2(a.y);
@@ -618,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc::fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < GC / 32; ++c) {
         uint32_t d[32];
         tc::tmem_ld32(dp_addr + c * 32, d);
         tc::tmem_wait_ld();
@@ -642,8 +660,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc::fence_after_sync();
       unsigned char* dq_row = reinterpret_cast<unsigned char*>(p.dq.ptr) +
                               2 * ((long long)b * p.dq.sb + (long long)h * p.dq.sh + (long long)qi * p.dq.ss) +
-                              128 * g;
-      store_half_row<IS_BF16>(lane_addr + kColAcc0 + 64 * g, dq_row, p.scale, live);
+                              2 * GC * g;
+      store_cols<IS_BF16>(lane_addr + kColAcc0 + GC * g, dq_row, p.scale, live);
     } else {
       failed = 1;
     }
@@ -731,7 +749,7 @@ extern "C" int ixb_fa_bwd(int dtype, const void* q, const void* k, const void* v
 
   cudaStream_t cs = (cudaStream_t)stream;
   const long long rows = n_bh * Sq;
-  kern_delta<<<(unsigned)((rows + 7) / 8), 256, 0, cs>>>(
+  kern_delta<<<(unsigned)((rows + 15) / 16), 256, 0, cs>>>(
       static_cast<const unsigned char*>(o), static_cast<const unsigned char*>(dout), delta, H, Sq, rows,
       o_strides[0], o_strides[1], o_strides[2], do_strides[0], do_strides[1], do_strides[2]);
   kern_dkv<<<(unsigned)(n_kv_tiles * n_bh), kThreads, kSmemBytes, cs>>>(mq, mk, mv, mdo, p);
