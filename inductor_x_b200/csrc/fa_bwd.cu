@@ -20,10 +20,16 @@
 // Warp 0 is the TMA producer, warp 1 the MMA issuer, the other 4 * NG warps do the
 // element-wise work in NG groups of four warps that split the 128 columns of a tile between
 // them (a warp may only touch the 32 TMEM lanes of its quadrant; no row reduction is needed
-// here - lse and delta come in precomputed - so the split costs nothing).  NG = 2 measured 4 %
-// faster than NG = 4 at 4096 keys: the kernels are bound by the hand-off chain of a tile, not
-// by the element-wise warps.  Every wait is bounded; a wait that gives up raises a flag in
-// `status` and lets the CTA drain and exit.
+// here - lse and delta come in precomputed - so the split costs nothing).  Every wait is
+// bounded; a wait that gives up raises a flag in `status` and lets the CTA drain and exit.
+//
+// Measured on B200 (4096 keys, causal): per 128 x 128 tile pair the tensor core needs about
+// 2050 cycles for the four products (one 128x128x16 MMA per 64 cycles, SS or TS form, one or
+// two issuing threads alike) and the element-wise warps about 2300 (the exponentials alone
+// fill the ex2 unit for 1024); with one tile in flight the two add up (4330 cycles per tile
+// pair).  A variant with 64-query sub-tiles, double-buffered score columns and a four-stage
+// ring overlapped them but ran 30 % slower: an SS-form MMA with N = 64 takes 48 cycles, not 32
+// (both operands come from shared memory at 128 bytes per cycle), and the hand-offs double.
 #include <atomic>
 #include "fa_maps.h"
 #include "ixb/tcgen05.cuh"
@@ -72,6 +78,13 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_bf16) 
 __device__ __forceinline__ float2 unpack_pair(uint32_t w, bool is_bf16) {
   if (is_bf16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
   return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// One arrival per warp: every lane has fenced its tensor-memory accesses, the warp
+// synchronises, lane 0 arrives (the barrier counts warps, not threads).
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) tc::mbar_arrive(bar);
 }
 
 // ------------------------------------------------------------------------------ delta
@@ -210,8 +223,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&p_full, kWorkers);
-    mbar_init(&ds_full, kWorkers);
+    mbar_init(&p_full, kWorkers / 32);
+    mbar_init(&ds_full, kWorkers / 32);
     mbar_init(&acc_done, 1);
     failed = 0;
     mbar_init_fence();
@@ -376,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc::tmem_wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(&p_full);
+      warp_arrive(&p_full, lane);
 
       if (!__all_sync(kFull, mbar_wait(&dp_full, it & 1, &failed))) {
         ok = false;
@@ -405,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc::tmem_wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(&ds_full);
+      warp_arrive(&ds_full, lane);
     }
 
     if (ok && n_it > 0) ok = mbar_wait(&acc_done, 0, &failed);
@@ -493,8 +506,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&s_read, kWorkers);
-    mbar_init(&ds_full, kWorkers);
+    mbar_init(&s_read, kWorkers / 32);
+    mbar_init(&ds_full, kWorkers / 32);
     mbar_init(&acc_done, 1);
     failed = 0;
     mbar_init_fence();
@@ -611,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int c = 0; c < GC / 32; ++c) tc::tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
       tc::tmem_wait_ld();
       tc::fence_before_sync();
-      tc::mbar_arrive(&s_read);
+      warp_arrive(&s_read, lane);
       const int col0 = j * BN + GC * g;
       const bool edge = (j * BN + BN > p.Sk) || (p.causal && (j * BN + BN - 1 > qt0 + diag));
       int lim = GC - 1;  // last visible key of this row, relative to this group's columns
@@ -652,7 +665,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc::tmem_wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(&ds_full);
+      warp_arrive(&ds_full, lane);
     }
 
     if (ok) ok = mbar_wait(&acc_done, 0, &failed);

@@ -67,11 +67,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           const volatile int* abort = nullptr) {
   if (mbar_test_wait(bar, parity)) return true;  // already complete: the common case on a hot path
-#ifdef EXP_SPIN
-#pragma unroll 1
-  for (int i = 0; i < (1 << 15); ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-#endif
 #pragma unroll 1
   for (int quick = 0; quick < 64; ++quick)
     if (mbar_try_wait(bar, parity)) return true;
