@@ -140,6 +140,9 @@ extern "C" {
 
 size_t ixb_outer_reduce_scratch_bytes(int64_t outer, int64_t inner, int rsplit) {
   if (rsplit <= 1 || outer <= 0 || inner <= 0) return 0;
+  // extents whose product does not fit are answered with the largest size: no buffer satisfies it
+  const size_t cap = SIZE_MAX / sizeof(float);
+  if ((size_t)inner > cap / (size_t)outer || (size_t)rsplit > cap / ((size_t)outer * (size_t)inner)) return SIZE_MAX;
   return (size_t)outer * (size_t)inner * (size_t)rsplit * sizeof(float);
 }
 
@@ -149,6 +152,8 @@ int ixb_outer_reduce(int dtype, int kind, const void* x, void* out, int64_t oute
   if (outer < 0 || R <= 0 || inner < 0) return IXB_ERR_ARG;
   if (outer == 0 || inner == 0) return IXB_OK;
   if (x == nullptr || out == nullptr) return IXB_ERR_ARG;
+  // outer * inner outputs, one thread each in the scalar paths: must fit a 32-bit grid of 256-thread CTAs
+  if (inner > (0x7fffffffLL * 256) / outer) return IXB_ERR_SHAPE;
   switch (dtype) {
     case IXB_F32: return outer_reduce_t<float>(kind, x, out, outer, R, inner, scratch, scratch_bytes, cfg, stream);
     case IXB_F16: return outer_reduce_t<ixb::f16>(kind, x, out, outer, R, inner, scratch, scratch_bytes, cfg, stream);
