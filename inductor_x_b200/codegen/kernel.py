@@ -1086,13 +1086,72 @@ class B200Kernel(SIMDKernel):
                         src.writeline(f"auto acc = Ctx::template splat_int<kVec>(Ctx::{iop}::id());")
                     else:
                         src.writeline(f"auto acc = Ctx::template splat<kVec>({red['op']}::identity());")
-                    src.writeline("#pragma unroll 8")  # independent loads of eight steps in flight
-                    src.writeline(f"for (long long r0_index = c.rbegin(); r0_index < {rnumel}; r0_index += c.rstep()) {{")
-                    with src.indent():
-                        src.splice(r_idx)
-                        src.splice(self._substitute(head, True))
-                        src.writeline(acc_line)
-                    src.writeline("}")
+                    import re
+
+                    head_text = self._substitute(head, True)
+                    # Full aligned tiles: the plain vector loads of eight reduced steps are issued
+                    # as raw 128-bit loads into an array before any of them is widened or used, so
+                    # that eight requests per thread are in flight whatever registers the compiler
+                    # would have spent on hoisting them itself (it keeps four to five).
+                    load_re = re.compile(r"^\s*const auto (tmp\d+) = ixb::gen::ldvec<(ixb::f16|ixb::bf16|float), kVec, FAST>"
+                                         r"\((.*), nvalid\);\s*$")
+                    loads, rest = [], []
+                    for line in head_text.splitlines():
+                        m = load_re.match(line)
+                        if m and not re.search(r"\btmp\d+\b", m.group(3)):
+                            loads.append(m.groups())
+                        else:
+                            rest.append(line)
+
+                    def plain_loop(start):
+                        src.writeline("#pragma unroll 8")
+                        src.writeline(f"for (long long r0_index = {start}; r0_index < {rnumel}; r0_index += c.rstep()) {{")
+                        with src.indent():
+                            src.splice(r_idx)
+                            src.splice(head_text)
+                            src.writeline(acc_line)
+                        src.writeline("}")
+
+                    if loads:
+                        src.writeline("if constexpr (FAST) {")
+                        with src.indent():
+                            src.writeline("long long rb = c.rbegin();")
+                            src.writeline(f"for (; rb + 7 * c.rstep() < {rnumel}; rb += 8 * c.rstep()) {{")
+                            with src.indent():
+                                for name, ctype, _ in loads:
+                                    src.writeline(f"{G}RawVec<{ctype}, kVec> raw_{name}[8];")
+                                src.writeline("#pragma unroll")
+                                src.writeline("for (int u = 0; u < 8; ++u) {")
+                                with src.indent():
+                                    src.writeline("const long long r0_index = rb + u * c.rstep();")
+                                    src.splice(r_idx)
+                                    for name, ctype, ptr in loads:
+                                        src.writeline(f"raw_{name}[u] = {G}ldraw<{ctype}, kVec>({ptr});")
+                                src.writeline("}")
+                                src.writeline("#pragma unroll")
+                                src.writeline("for (int u = 0; u < 8; ++u) {")
+                                with src.indent():
+                                    for name, _, _ in loads:
+                                        src.writeline(f"{G}pin(raw_{name}[u]);")
+                                src.writeline("}")
+                                src.writeline("#pragma unroll")
+                                src.writeline("for (int u = 0; u < 8; ++u) {")
+                                with src.indent():
+                                    src.writeline("const long long r0_index = rb + u * c.rstep();")
+                                    src.splice(r_idx)
+                                    for name, ctype, _ in loads:
+                                        src.writeline(f"const auto {name} = {G}widen_raw(raw_{name}[u]);")
+                                    src.splice("\n".join(rest))
+                                    src.writeline(acc_line)
+                                src.writeline("}")
+                            src.writeline("}")
+                            plain_loop("rb")
+                        src.writeline("} else {")
+                        with src.indent():
+                            plain_loop("c.rbegin()")
+                        src.writeline("}")
+                    else:
+                        plain_loop("c.rbegin()")
                     src.splice(self._substitute(tail, True))
                 src.writeline("}")
             elif self.is_row:

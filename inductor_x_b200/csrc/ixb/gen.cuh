@@ -188,6 +188,36 @@ __device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type ldvec(
   for (int i = 0; i < N; ++i) r.v[i] = i < nvalid ? Mem<T>::ld(p + i) : V();
   return r;
 }
+// A run of N elements as the raw 128-bit words it was loaded as: what a thread holds while
+// several independent loads are in flight, before any of them is widened.
+template <class T, int N> struct RawVec {
+  static constexpr int kWords = N * (int)sizeof(T) / 16;
+  static_assert(kWords >= 1 && kWords * 16 == N * (int)sizeof(T), "whole 128-bit words");
+  uint4 q[kWords];
+};
+// complete, 16-byte aligned run (the caller has established both), read once: no L1 allocation
+template <class T, int N> __device__ __forceinline__ RawVec<T, N> ldraw(const T* p) {
+  RawVec<T, N> r;
+#pragma unroll
+  for (int c = 0; c < RawVec<T, N>::kWords; ++c) r.q[c] = ldg_stream(p + c * (16 / (int)sizeof(T)));
+  return r;
+}
+// Placed after a batch of ldraw calls: the words of `raw` cannot be consumed before this
+// point, and (volatile statements keep their order) this point comes after every load of the
+// batch - so all of them are issued before the first result is waited for.
+template <class T, int N> __device__ __forceinline__ void pin(RawVec<T, N>& raw) {
+#pragma unroll
+  for (int c = 0; c < RawVec<T, N>::kWords; ++c)
+    asm volatile("" : "+r"(raw.q[c].x), "+r"(raw.q[c].y), "+r"(raw.q[c].z), "+r"(raw.q[c].w));
+}
+template <class T, int N>
+__device__ __forceinline__ typename vec_of<typename Mem<T>::val, N>::type widen_raw(const RawVec<T, N>& raw) {
+  typename vec_of<typename Mem<T>::val, N>::type r;
+  constexpr int kPer = 16 / (int)sizeof(T);
+#pragma unroll
+  for (int c = 0; c < RawVec<T, N>::kWords; ++c) unpack<T>(raw.q[c], &r.v[c * kPer]);
+  return r;
+}
 template <class T, int N, bool FAST = false, class A>
 __device__ __forceinline__ void stvec(T* p, int nvalid, const A& val) {
   using V = typename Mem<T>::val;
@@ -1206,13 +1236,15 @@ template <int V, int TX, int TY> struct OuterCtx {
             if (h * HV + i < V) ipart[(warp * TX + tx) * HV + i] = r.v[h * HV + i];
         }
         __syncthreads();
+        if (writer()) {
 #pragma unroll
-        for (int i = 0; i < HV; ++i) {
-          if (h * HV + i < V) {
-            long long a = ipart[tx * HV + i];
+          for (int i = 0; i < HV; ++i) {
+            if (h * HV + i < V) {
+              long long a = ipart[tx * HV + i];
 #pragma unroll
-            for (int w = 1; w < kWarps; ++w) a = IOp::f(a, ipart[(w * TX + tx) * HV + i]);
-            r.v[h * HV + i] = a;
+              for (int w = 1; w < kWarps; ++w) a = IOp::f(a, ipart[(w * TX + tx) * HV + i]);
+              r.v[h * HV + i] = a;
+            }
           }
         }
         __syncthreads();
@@ -1220,7 +1252,7 @@ template <int V, int TX, int TY> struct OuterCtx {
     }
     return r;
   }
-  // fold the TY partial vectors; every thread row receives the result
+  // fold the TY partial vectors; the writer row receives the result
   template <class Op> __device__ __forceinline__ vf<V> combine(const vf<V>& acc) {
     vf<V> r = acc;
 #pragma unroll
@@ -1234,12 +1266,17 @@ template <int V, int TX, int TY> struct OuterCtx {
         for (int i = 0; i < V; ++i) part[(warp * TX + tx) * V + i] = r.v[i];
       }
       __syncthreads();
+      // only the thread row that stores the tile needs the folded vector (a generated outer
+      // kernel has one reduction and nothing after it but the store): the other rows skip
+      // the kWarps x V shared-memory reads
+      if (writer()) {
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        float a = part[tx * V + i];
+        for (int i = 0; i < V; ++i) {
+          float a = part[tx * V + i];
 #pragma unroll
-        for (int w = 1; w < kWarps; ++w) a = Op::combine(a, part[(w * TX + tx) * V + i]);
-        r.v[i] = a;
+          for (int w = 1; w < kWarps; ++w) a = Op::combine(a, part[(w * TX + tx) * V + i]);
+          r.v[i] = a;
+        }
       }
       __syncthreads();
     }
