@@ -1159,8 +1159,12 @@ class B200Kernel(SIMDKernel):
 
                 cfg = self._row_cfg
                 tiling = self._short_row_tiling()
+                # rows of a whole 128-byte line or more: the output digit runs fastest inside a tile
+                b_first = tiling is not None and \
+                    self._static_numel("r0_") * config_bytes(self._narrowest_node_dtype()) >= 128
                 slot_line = ("const long long xindex = xslot;" if tiling is None else
-                             f"const long long xindex = {G}tile_order<{tiling[0]}, {tiling[1]}, 16, 16>(xslot);")
+                             f"const long long xindex = {G}tile_order<{tiling[0]}, {tiling[1]}, 16, 16, "
+                             f"{'true' if b_first else 'false'}>(xslot);")
                 row_body = re.sub(r"@B\d+@\n?", "", self._substitute(body_text, False))
                 # per-column operands, most used first: the first IXB_ROW_KREGS of them are
                 # registers, the others are read from the shared-memory table

@@ -1043,14 +1043,17 @@ __device__ __forceinline__ vf<E> kget(const Ctx& c, const vf<E>& reg) {
 // LC digits fastest, then TB consecutive LB digits - makes a warp read adjacent rows (one
 // contiguous span) and lets the one-element-per-row results of a tile fill whole sectors, the
 // job the reference gives its transposed tile (inductor_x/codegen/triton.py:856-888).
-template <int LB, int LC, int TB, int TC>
+// B_FIRST: inside a tile the output digit runs fastest, so the rows a warp works on at once
+// store one contiguous run (a full 32-byte sector for sixteen 16-bit results); chosen when a
+// row is at least one 128-byte line, i.e. when reading rows that are far apart wastes nothing.
+template <int LB, int LC, int TB, int TC, bool B_FIRST = false>
 __device__ __forceinline__ long long tile_order(long long slot) {
   static_assert(LB % TB == 0 && LC % TC == 0, "tiles must divide both extents");
   constexpr long long kPlane = (long long)LB * LC;
   const long long a = slot / kPlane;
   const int rem = (int)(slot % kPlane);
-  const int c_lo = rem % TC;
-  const int b_lo = (rem / TC) % TB;
+  const int c_lo = B_FIRST ? (rem / TB) % TC : rem % TC;
+  const int b_lo = B_FIRST ? rem % TB : (rem / TC) % TB;
   const int b_hi = (rem / (TC * TB)) % (LB / TB);
   const int c_hi = rem / (TC * LB);
   return a * kPlane + (long long)(c_hi * TC + c_lo) * LB + (b_hi * TB + b_lo);
