@@ -4,13 +4,15 @@
 // (inductor_x/npu_fusion_attention_graph.py:20-35).
 //
 // One CTA owns two 128-row query tiles (A, B) of one (batch, head) and walks the
-// key/value tiles (128 keys each) that they can see.  Ten warps, three roles:
+// key/value tiles (128 keys each) that they can see.  Eleven warps, four roles:
 //   warp 0     TMA producer: Q once, then K_j / V_j into two-stage rings
 //   warp 1     MMA issuer: S_t(j) = Q_t K_j^T into tile t's TMEM buffer, then
 //              O_t += P_t(j) V_j with P read straight from TMEM (it overwrites S as 16-bit
 //              values).  The two tiles alternate, so the tensor core works on one tile
 //              while the other tile's softmax runs.
 //   warps 2-5  softmax of tile A, warps 6-9 softmax of tile B: thread <-> query row.
+//   warp 10    forwarder: waits for the K/V tiles of a step and adds its arrival to the
+//              tiles' P barriers, so that the issuer makes one wait per tile and step
 //              Pass 1 reads the S row for its maximum; pass 2 re-reads it 32 columns at
 //              a time, exponentiates and writes P back.  The O accumulator is rescaled
 //              only when the maximum has grown by more than 2^8 since the last rescale
@@ -35,7 +37,7 @@ constexpr int HD = 128;          // head dimension
 constexpr int kStages = 2;
 constexpr int kTileBytes = BN * HD * 2;     // one operand tile, 16-bit elements
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column TMA box of the tile
-constexpr int kThreads = 64 + NQ * 128;
+constexpr int kThreads = 64 + NQ * 128 + 32;  // producer, issuer, softmax warps, forwarder
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;  // + 128 * tile
 constexpr float kRescaleThreshold = 8.f;    // log2 units
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int t = 0; t < NQ; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 128);
+      mbar_init(&p_full[t], 128 + 1);  // the rows of the tile and the forwarder
       mbar_init(&pv_done[t], 1);
     }
     failed = 0;
@@ -203,7 +205,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                      (accumulate || ks > 0) ? 1u : 0u);
         }
       };
-      int v_seen = -1, k_seen = 0;  // key tiles whose V / K arrival has been waited for
       bool ok = mbar_wait(&q_full, 0, &failed);
       if (ok && n_kv > 0) ok = mbar_wait(&k_full[0], 0, &failed);
       if (ok && n_kv > 0) {
@@ -225,17 +226,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           // every wait of this tile's step comes first, so that its sixteen MMAs go to the
           // tensor core back to back and its queue does not drain in between
           const bool do_pv = j < n_kv_t[t], do_qk = j + 1 < n_kv_t[t];
-          if (do_pv) {
-            ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
-            if (v_seen != j) {  // a stage is waited for once, not once per tile
-              ok = ok && mbar_wait(&v_full[s], n & 1, &failed);
-              v_seen = j;
-            }
-          }
-          if (do_qk && k_seen != j + 1) {
-            ok = ok && mbar_wait(&k_full[s1], n1 & 1, &failed);
-            k_seen = j + 1;
-          }
+          // one wait per tile and step: the forwarder warp has added its arrival to p_full
+          // only after V_j and K_(j+1) landed, so this thread - for which every wait costs
+          // about 240 cycles beside the busy softmax warps of the other tile - does not wait
+          // for the operand rings itself
+          if (do_pv) ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
           if (!ok) break;
           tc::fence_after_sync();
           if (do_pv) {
@@ -252,6 +247,29 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         tc::mma_commit(&v_empty[s]);
         if (j + 1 < n_kv) tc::mma_commit(&k_empty[s1]);
+      }
+      if (!ok) failed = 1;
+    }
+    __syncwarp();
+  } else if (warp == 2 + NQ * 4) {
+    // ------------------------------------------------------------------ forwarder
+    // Waits for the operand tiles of a step on behalf of the MMA issuer and adds one arrival
+    // to p_full of every tile that has work in the step.
+    if (lane == 0) {
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1, n = j >> 1;
+        const int s1 = (j + 1) & 1, n1 = (j + 1) >> 1;
+        ok = mbar_wait(&v_full[s], n & 1, &failed);
+        if (ok && j + 1 < n_kv) ok = mbar_wait(&k_full[s1], n1 & 1, &failed);
+        if (!ok) break;
+#pragma unroll
+        for (int t = 0; t < NQ; ++t)
+          if (j < n_kv_t[t]) tc::mbar_arrive(&p_full[t]);
+        // not ahead of the rows: the arrival for step j + 1 must not fall into phase j
+#pragma unroll
+        for (int t = 0; t < NQ; ++t)
+          if (j < n_kv_t[t]) ok = ok && mbar_wait(&p_full[t], j & 1, &failed);
       }
       if (!ok) failed = 1;
     }
