@@ -235,7 +235,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc::fence_after_sync();
           if (do_pv) {
             issue_pv(t, s, j > 0);
-            tc::mma_commit(&pv_done[t]);
+            // only the last product of the tile needs a signal of its own: every earlier one
+            // is covered by the commit behind the scores that follow it (a commit tracks all
+            // MMAs issued before it)
+            if (!do_qk) tc::mma_commit(&pv_done[t]);
           }
           if (do_qk) {
             // P_t(j) has been consumed by the MMAs just issued (the tensor core runs
@@ -330,12 +333,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float f = !grow ? 1.f : ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new));
         l *= f;
         if (j > 0) {
-          // O may only be touched once O += P(j-1) V(j-1) has completed
-          if (!__all_sync(kFull, mbar_wait(&pv_done[t], (j - 1) & 1, &failed))) {
-            ok = false;
-            break;
-          }
-          tc::fence_after_sync();
+          // O may only be touched once O += P(j-1) V(j-1) has completed: it has - S(j),
+          // which this warp has waited for, was committed behind it
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t o[32];
@@ -387,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc::mbar_arrive(&p_full[t]);
     }
 
-    if (ok && my_n_kv > 0) ok = mbar_wait(&pv_done[t], (my_n_kv - 1) & 1, &failed);
+    if (ok && my_n_kv > 0) ok = mbar_wait(&pv_done[t], 0, &failed);  // the tile's last product
     ok = __all_sync(kFull, ok);
     if (ok) {
       tc::fence_after_sync();
