@@ -41,7 +41,7 @@ using namespace ixb;
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr int HD = 128;  // head dimension
-constexpr int kStages = 2;
+constexpr int kStages = 2;  // (the issuers pick stage descriptors with two-way selects: no local-memory arrays)
 constexpr int kTileBytes = 128 * HD * 2;
 constexpr int kHalfBytes = kTileBytes / 2;
 constexpr int NG = 2;             // groups of element-wise warps; each takes 128 / NG columns of a tile
@@ -305,22 +305,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = mbar_wait(&p_full, it & 1, &failed);
         if (!ok) break;
         tc::fence_after_sync();
-        issue_ts(t_dv, t_s, do_desc_mn[s], idesc_mn, it > 0);  // dV += P^T dO
+        issue_ts(t_dv, t_s, (s ? do_desc_mn[1] : do_desc_mn[0]), idesc_mn, it > 0);  // dV += P^T dO
         if (next) {
           ok = mbar_wait(&qdo_full[s1], ((it + 1) >> 1) & 1, &failed);
           if (!ok) break;
           tc::fence_after_sync();
           // the tensor core runs its MMAs in order: P^T has been consumed when this one starts
-          issue_ss(t_s, k_desc, q_desc[s1], idesc_kk);
+          issue_ss(t_s, k_desc, (s1 ? q_desc[1] : q_desc[0]), idesc_kk);
           tc::mma_commit(&s_full);
         }
         ok = mbar_wait(&ds_full, it & 1, &failed);
         if (!ok) break;
         tc::fence_after_sync();
-        issue_ts(t_dk, t_dp, q_desc_mn[s], idesc_mn, it > 0);  // dK += dS^T Q
+        issue_ts(t_dk, t_dp, (s ? q_desc_mn[1] : q_desc_mn[0]), idesc_mn, it > 0);  // dK += dS^T Q
         tc::mma_commit(&qdo_empty[s]);
         if (next) {
-          issue_ss(t_dp, v_desc, do_desc[s1], idesc_kk);
+          issue_ss(t_dp, v_desc, (s1 ? do_desc[1] : do_desc[0]), idesc_kk);
           tc::mma_commit(&dp_full);
         }
       }
@@ -575,19 +575,19 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = ok && mbar_wait(&k_full[s1], n1 & 1, &failed);
           if (!ok) break;
           tc::fence_after_sync();
-          issue_ss(t_s, q_desc, k_desc[s1], idesc_kk);
+          issue_ss(t_s, q_desc, (s1 ? k_desc[1] : k_desc[0]), idesc_kk);
           tc::mma_commit(&s_full);
         }
         ok = mbar_wait(&ds_full, j & 1, &failed);
         if (!ok) break;
         tc::fence_after_sync();
-        issue_ts(t_dq, t_dp, k_desc_mn[s], idesc_mn, j > 0);  // dQ += dS K
+        issue_ts(t_dq, t_dp, (s ? k_desc_mn[1] : k_desc_mn[0]), idesc_mn, j > 0);  // dQ += dS K
         tc::mma_commit(&k_empty[s]);
         if (next) {
           ok = mbar_wait(&v_full[s1], n1 & 1, &failed);
           if (!ok) break;
           tc::fence_after_sync();
-          issue_ss(t_dp, do_desc, v_desc[s1], idesc_kk);  // after dQ(j): dS(j) has been consumed
+          issue_ss(t_dp, do_desc, (s1 ? v_desc[1] : v_desc[0]), idesc_kk);  // after dQ(j): dS(j) has been consumed
           tc::mma_commit(&dp_full);
           tc::mma_commit(&v_empty[s1]);
         }

@@ -34,7 +34,7 @@ constexpr int BM = 128;          // rows of one query tile
 constexpr int NQ = 2;            // query tiles per CTA
 constexpr int BN = 128;          // keys per tile
 constexpr int HD = 128;          // head dimension
-constexpr int kStages = 2;
+constexpr int kStages = 2;  // (the issuer picks stage descriptors with two-way selects)
 constexpr int kTileBytes = BN * HD * 2;     // one operand tile, 16-bit elements
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column TMA box of the tile
 constexpr int kThreads = 64 + NQ * 128 + 32;  // producer, issuer, softmax warps, forwarder
@@ -183,12 +183,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         k_desc[s] = tc::smem_desc(smem_u32(k_smem + (size_t)s * kTileBytes), 16, 1024);
         v_desc[s] = tc::smem_desc(smem_u32(v_smem + (size_t)s * kTileBytes), kHalfBytes, 1024);
       }
+      // (descriptors are picked with selects: an array indexed by the run-time stage would
+      // live in local memory, and every load of it would sit on this thread's critical path)
       auto issue_qk = [&](int t, int stage) {
         const uint32_t d = tmem_base + kColS + t * 128;
+        const uint64_t qd = t ? q_desc[1] : q_desc[0];
+        const uint64_t kd = stage ? k_desc[1] : k_desc[0];
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-          tc::mma_ss(d, q_desc[t] + off, k_desc[stage] + off, idesc_qk, ks > 0);
+          tc::mma_ss(d, qd + off, kd + off, idesc_qk, ks > 0);
         }
       };
       // O_t += P_t V_j: A = P from TMEM (two 16-bit values per column, 8 columns per step),
@@ -199,9 +203,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t a = tmem_base + kColS + t * 128;
         const uint32_t d = tmem_base + kColO + t * 128;
+        const uint64_t vd = stage ? v_desc[1] : v_desc[0];
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          tc::mma_ts(d, a + ks * 8, v_desc[stage] + (uint32_t)(ks * 2048 >> 4), idesc_pv,
+          tc::mma_ts(d, a + ks * 8, vd + (uint32_t)(ks * 2048 >> 4), idesc_pv,
                      (accumulate || ks > 0) ? 1u : 0u);
         }
       };
