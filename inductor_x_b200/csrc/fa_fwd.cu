@@ -313,7 +313,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         lim = last - col0;
       }
       // ---- pass 1: row maximum of the raw scores, two 64-column round trips
-      float mx = -INFINITY;
+      // (four independent chains: one chain of 64 dependent max3 would cost its latency 64 times)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t raw[64];
@@ -323,13 +324,14 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (edge) {
 #pragma unroll
           for (int e = 0; e < 64; ++e)
-            mx = fmaxf(mx, (hh * 64 + e <= lim) ? __uint_as_float(raw[e]) : -INFINITY);
+            mx4[e & 3] = fmaxf(mx4[e & 3], (hh * 64 + e <= lim) ? __uint_as_float(raw[e]) : -INFINITY);
         } else {
 #pragma unroll
           for (int e = 0; e < 64; e += 2)
-            mx = max3(mx, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
+            mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
         }
       }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= p.scale_log2;  // scale > 0: scaling commutes with the maximum
       // lazy rescale: move the reference maximum only when it would grow by > 2^8
       const bool grow = mx > m_used + kRescaleThreshold;  // also true for the first tile
@@ -358,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nm2 = make_float2(-mref, -mref);
-      float2 sum2 = make_float2(0.f, 0.f);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // two chains of packed adds
       uint32_t buf[2][32];
       tc::tmem_ld32(s_addr, buf[0]);
       tc::tmem_wait_ld();
@@ -379,13 +381,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (col > lim) pe.x = 0.f;
             if (col + 1 > lim) pe.y = 0.f;
           }
-          sum2 = add2(sum2, pe);
+          sum2[(e >> 1) & 1] = add2(sum2[(e >> 1) & 1], pe);
           pk[e / 2] = pack_pair(pe.x, pe.y, IS_BF16);
         }
         tc::tmem_wait_ld();
         tc::tmem_st16(s_addr + c * 16, pk);
       }
-      l += sum2.x + sum2.y;
+      l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       tc::tmem_wait_st();
       tc::fence_before_sync();
       tc::mbar_arrive(&p_full[t]);
