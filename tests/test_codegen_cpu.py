@@ -145,6 +145,11 @@ def test_strided_reduction_over_contiguous_outputs_uses_outer_mapping(dry_backen
     # each warp walks the reduced axis
     assert "launch_outer_gen<Body, 8>" in code and "family='outer'" in code
     assert "c.template combine<ixb::MaxOp>(acc)" in code
+    # full aligned tiles issue the loads of eight reduced steps as raw 128-bit words and pin
+    # them before the first is widened; ragged tiles keep the plain loop
+    assert "if constexpr (FAST)" in code and "RawVec<ixb::f16, kVec> raw_tmp0[8];" in code
+    assert "ixb::gen::ldraw<ixb::f16, kVec>(" in code and "ixb::gen::pin(raw_tmp0[u]);" in code
+    assert "ixb::gen::widen_raw(raw_tmp0[u])" in code
     # an inner-axis reduction of the same tensor keeps the row mapping
     code = generated(lambda t: t.amax(-1), x)
     assert "launch_row_gen<" in code and "launch_outer_gen" not in code
@@ -237,3 +242,16 @@ def test_registration_surface():
     q = torch.empty(2, 4, 16, 128, device="meta", dtype=torch.bfloat16)
     out = torch.ops.b200_graph.b200_fa(q, q, q, 4, "BNSD")
     assert out[0].shape == q.shape and out[1].shape == (2, 4, 16, 8) and len(out) == 7
+
+
+def test_short_rows_of_a_whole_line_walk_the_output_digit_first(dry_backend):
+    """Config 3a's sum: rows of 128 bytes that are far apart along the output's fastest digit.
+    The kept index is walked in 16 x 16 tiles with the OUTPUT digit fastest inside a tile (the
+    sixteen rows a warp works on store one 32-byte sector); rows shorter than a line keep the
+    input-contiguous order."""
+    x = torch.randn(4, 32, 64, 64).half()
+    code = generated(lambda t: t.permute(0, 2, 1, 3).sum(3), x)
+    assert "ixb::gen::tile_order<32, 64, 16, 16, true>(xslot)" in code
+    x = torch.randn(4, 32, 64, 16).half()
+    code = generated(lambda t: t.permute(0, 2, 1, 3).sum(3), x)
+    assert "tile_order<32, 64, 16, 16, false>(xslot)" in code
