@@ -544,6 +544,34 @@ class B200Kernel(SIMDKernel):
             self.inside_reduction = prior
             self.compute = compute
 
+    # ------------------------------------------------------------------ scans
+    def scan(self, dtypes, combine_fn, values):
+        """Inclusive prefix sum along a stride-1 row held by a team (``cumsum`` over the last
+        axis; the reference keeps it an extern kernel, ``inductor_x/lowering.py:235-245``).
+        Other combine functions, several values, looped or strided rows are refused; the
+        lowering only sends the supported form here."""
+        assert self.inside_reduction and self.is_row
+        if len(values) != 1 or self.looped or self._is_dynamic("r0_"):
+            raise UnsupportedByTemplates("scan: one value over a static row held on chip only")
+        if dtypes[0] not in (torch.float32, torch.float16, torch.bfloat16):
+            raise UnsupportedByTemplates(f"scan of {dtypes[0]}")
+        # which combine function is it?  run it on two probes and read the op off the value table
+        a = self.cse.newvar(dtype=torch.float32)
+        b = self.cse.newvar(dtype=torch.float32)
+        probe = IndentedBuffer()
+        saved = self.compute
+        self.compute = probe
+        try:
+            (res,) = combine_fn((a,), (b,))
+        finally:
+            self.compute = saved
+        operands = self.op_of(res, "add")
+        if operands is None or {str(o) for o in operands} != {str(a), str(b)}:
+            raise UnsupportedByTemplates("scan: only sums are scanned by the row template")
+        self._has_scan = True
+        out = self.cse.generate(self.compute, f"c.scan_sum({values[0]})", dtype=torch.float32)
+        return (out,)
+
     # ------------------------------------------------------------------ reductions
     def _reduction_marker(self, tag: str) -> None:
         self.compute.writeline(f"@B{tag[2:]}")  # marks where the reduction loop of the outer mapping ends

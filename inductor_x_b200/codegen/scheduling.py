@@ -34,8 +34,10 @@ class B200Scheduling(SIMDScheduling):
     @classmethod
     def get_backend_features(cls, device):
         # no tuple reductions: var_mean is lowered to the two-pass form, as the reference
-        # does (inductor_x/lowering.py:270-325); no scans / sorts / foreach
-        return OrderedSet([BackendFeature.INPLACE_BUFFERS, BackendFeature.REDUCE_TO_SINGLE_ELEMENT])
+        # does (inductor_x/lowering.py:270-325); scans only in the form the lowering lets
+        # through (a sum along a stride-1 row held on chip); no sorts / foreach
+        return OrderedSet([BackendFeature.INPLACE_BUFFERS, BackendFeature.REDUCE_TO_SINGLE_ELEMENT,
+                           BackendFeature.SCAN])
 
     @classmethod
     def get_tiling_and_scores(cls, node_schedule, numel, reduction_numel=sympy.S.One,

@@ -682,6 +682,56 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     }
   }
 
+  // ---- inclusive prefix sum along the row (cumsum over the stride-1 axis) ----------------------
+  // Row order: vector i of thread t is vector i * TEAM + t of the row.  Per round i every
+  // thread scans its own vector, the vector totals are scanned over the team in thread order
+  // (shuffles inside a warp, one slot per warp across warps), and the total of the rounds
+  // before is carried along.  fp32 accumulation, as the reference's sums.
+  template <class A> __device__ __forceinline__ vf<kE> scan_sum(const A& val) {
+    vf<kE> out;
+    float carry = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float run = 0.f;
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j) {
+        run += inside(i, j) ? Cast<float>::from(at(val, i * Base::kVec + j)) : 0.f;
+        out.v[i * Base::kVec + j] = run;
+      }
+      // inclusive scan of `run` over the lanes of this thread's warp (or lane group)
+      float incl = run;
+      const int wl = this->lane & (kGroup - 1);
+#pragma unroll
+      for (int off = 1; off < kGroup; off <<= 1) {
+        const float up = __shfl_up_sync(kFull, incl, off, kGroup);
+        if (wl >= off) incl += up;
+      }
+      float before = incl - run;                                  // lanes ahead of this one
+      float total = __shfl_sync(kFull, incl, kGroup - 1, kGroup);  // the warp's (group's) total
+      if constexpr (TEAM > 32) {
+        float* slot = slot_base();
+        const int w = this->lane >> 5;
+        if ((this->lane & 31) == 31) slot[w * 4] = incl;
+        team_barrier(this->team + 1, TEAM);
+        float ahead = 0.f, all = 0.f;
+#pragma unroll
+        for (int k = 0; k < kW; ++k) {
+          const float tk = slot[k * 4];
+          if (k < w) ahead += tk;
+          all += tk;
+        }
+        before += ahead;
+        total = all;
+        this->phase ^= 1;
+      }
+      const float base = carry + before;
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] += base;
+      carry += total;
+    }
+    return out;
+  }
+
   // ---- thread-local folds -------------------------------------------------------------------
   template <class A> __device__ __forceinline__ float local_sum(const A& val) const {
     if constexpr (FULL && op::is_fvec<A>::value) {

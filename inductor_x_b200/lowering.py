@@ -9,7 +9,8 @@ What changed underneath.  The reference whitelists ~50 aten ops (``GENERATE_LIST
 ``:80-148``) and turns *everything else* into an extern call, so e.g. ``gelu``, ``sigmoid``,
 ``pow``, ``sin/cos`` and ``index_select`` break fusion.  Here the templates instantiate any
 pointwise / reduction / indexing body, so the policy is inverted: only the op families no
-template exists for (scans, sorts, random numbers, scatter with a reduction other than add)
+template exists for (sorts, random numbers, scatter with a reduction other than add, and every
+scan except a floating ``cumsum`` along the last axis, which the row template scans on chip)
 are forced to extern kernels; accumulating scatters (``index_put(accumulate=True)``,
 ``scatter_add``, ``index_add``) are generated with atomic adds.  The reference's special lowerings are not carried over where they encode
 bugs or NPU workarounds: ``sum_`` always returning fp32 (``:204-215``), the hard-coded
@@ -30,7 +31,7 @@ prims = torch.ops.prims
 
 # op families without a B200 template: they stay extern (ATen) kernels
 FALLBACK_LIST = [
-    aten.cumsum, aten.cumprod, aten.cummax, aten.cummin, aten.logcumsumexp,
+    aten.cumprod, aten.cummax, aten.cummin, aten.logcumsumexp,
     aten.sort, aten.topk, aten.scatter_reduce, aten.bernoulli, aten.rand, aten.randn, aten.randint, aten.randperm,
     aten.native_dropout, aten.multinomial, aten.bucketize, aten.searchsorted, aten.histc,
 ]
@@ -69,9 +70,50 @@ def _init_set(input_list, output_set):
                 output_set.add(other)
 
 
+#: longest row a scan keeps on chip (elements); longer rows stay with the extern kernel
+MAX_SCAN_ROW = 16384
+
+
+def _row_scan_ok(x, axis, dtype) -> bool:
+    """cumsum cases the row template scans: a floating sum along the last axis of a row that a
+    team holds on chip.  Everything else - other axes (the MoE gating graph scans along the
+    token axis), integer inputs, very long or dynamic rows - stays an extern kernel, which is
+    all the reference does for cumsum (``inductor_x/lowering.py:235-245``)."""
+    size = x.get_size()
+    if len(size) == 0 or x.get_dtype() not in (torch.float32, torch.float16, torch.bfloat16):
+        return False
+    if dtype is not None and dtype != x.get_dtype():
+        return False
+    if axis is None or axis % len(size) != len(size) - 1:
+        return False
+    try:
+        n = int(size[-1])
+    except (TypeError, ValueError):
+        return False
+    return 2 <= n <= MAX_SCAN_ROW
+
+
+def _install_cumsum_lowering():
+    """Stock scan lowering for the supported form, extern kernel otherwise."""
+    op = aten.cumsum.default
+    stock = lowerings.get(op)
+    if stock is None or getattr(stock, "_ixb_guarded", False):
+        return
+    extern = lowering.fallback_handler(op, add_to_fallback_set=False)
+
+    def cumsum(x, axis=None, *, dtype=None):
+        if _row_scan_ok(x, axis, dtype):
+            return stock(x, axis, dtype=dtype)
+        return extern(x, axis, dtype=dtype)
+
+    cumsum._ixb_guarded = True
+    lowerings[op] = cumsum
+
+
 def _register_b200_inductor_fallbacks():
     """Force the op families in ``FALLBACK_LIST`` to extern kernels.  Returns the overloads
     that were switched."""
+    _install_cumsum_lowering()
     targets = set()
     _init_set(FALLBACK_LIST, targets)
     switched = []

@@ -255,3 +255,18 @@ def test_short_rows_of_a_whole_line_walk_the_output_digit_first(dry_backend):
     x = torch.randn(4, 32, 64, 16).half()
     code = generated(lambda t: t.permute(0, 2, 1, 3).sum(3), x)
     assert "tile_order<32, 64, 16, 16, false>(xslot)" in code
+
+
+def test_cumsum_over_the_last_axis_is_scanned_by_the_row_template(dry_backend):
+    """A floating cumsum along the stride-1 axis becomes a row kernel with a team-wide prefix
+    sum (fused with the pointwise work around it); other axes and integer inputs stay extern
+    kernels, which is all the reference does for cumsum (inductor_x/lowering.py:235-245)."""
+    x = torch.randn(64, 1024)
+    code = generated(lambda t: torch.cumsum(t * 2.0, -1) + 1.0, x)
+    assert code.count("ixb_load_kernel('''") == 1 and "c.scan_sum(" in code and "launch_row_gen<" in code
+    extern = "torch.ops.aten.cumsum.default("
+    assert extern not in code
+    code = generated(lambda t: torch.cumsum(t, 0), x)
+    assert "c.scan_sum(" not in code and extern in code
+    code = generated(lambda t: torch.cumsum(t, -1), torch.arange(64 * 128).reshape(64, 128))
+    assert "c.scan_sum(" not in code and extern in code

@@ -573,3 +573,29 @@ def test_rows_longer_than_a_team_are_walked_in_chunks(cuda):
     assert code.count("ixb_load_kernel('''") == 1
     want = F.layer_norm(xb.double(), (100000,), ga.double(), be.double())
     assert graphs.max_rel_err(out.cpu().double(), want.cpu()) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(64, 1024), (37, 1000), (8, 4096), (300, 24), (5, 16384), (3, 7, 130)])
+def test_cumsum_over_the_last_axis_is_scanned_on_chip(cuda, dtype, shape):
+    """cumsum along the stride-1 axis: one row kernel with a team-wide prefix sum, fused with
+    the pointwise work before and after it (the reference leaves cumsum to an extern kernel,
+    inductor_x/lowering.py:235-245).  fp32 accumulation: rel 1e-5 for fp32, 2e-2 for bf16,
+    against a float64 scan of the same (rounded) inputs; ragged rows, sub-warp teams and rows
+    of 16384 elements (1024 threads x 4 vectors) included."""
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g).to(dtype)
+    fn = lambda t: torch.cumsum(t * 0.5, -1) + 1.0
+    got, code = compile_and_code(fn, x.to(cuda))
+    assert code.count("ixb_load_kernel('''") == 1 and "c.scan_sum(" in code
+    assert "torch.ops.aten.cumsum.default(" not in code
+    want = torch.cumsum(x.double() * 0.5, -1) + 1.0
+    assert got.dtype == dtype
+    assert graphs.max_rel_err(got.cpu().double(), want) <= graphs.tolerance(dtype)
+
+
+def test_cumsum_along_other_axes_stays_extern(cuda):
+    x = torch.randn(512, 64, device=cuda)
+    got, code = compile_and_code(lambda t: torch.cumsum(t, 0) * 2.0, x)
+    assert "torch.ops.aten.cumsum.default(" in code and "c.scan_sum(" not in code
+    torch.testing.assert_close(got, torch.cumsum(x, 0) * 2.0, rtol=1e-5, atol=1e-5)
