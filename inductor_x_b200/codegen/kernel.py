@@ -553,11 +553,13 @@ class B200Kernel(SIMDKernel):
         assert self.inside_reduction and self.is_row
         if len(values) != 1 or self.looped or self._is_dynamic("r0_"):
             raise UnsupportedByTemplates("scan: one value over a static row held on chip only")
-        if dtypes[0] not in (torch.float32, torch.float16, torch.bfloat16):
+        is_int = dtypes[0] in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.bool)
+        if not is_int and dtypes[0] not in (torch.float32, torch.float16, torch.bfloat16):
             raise UnsupportedByTemplates(f"scan of {dtypes[0]}")
         # which combine function is it?  run it on two probes and read the op off the value table
-        a = self.cse.newvar(dtype=torch.float32)
-        b = self.cse.newvar(dtype=torch.float32)
+        probe_dtype = torch.int64 if is_int else torch.float32
+        a = self.cse.newvar(dtype=probe_dtype)
+        b = self.cse.newvar(dtype=probe_dtype)
         probe = IndentedBuffer()
         saved = self.compute
         self.compute = probe
@@ -569,7 +571,10 @@ class B200Kernel(SIMDKernel):
         if operands is None or {str(o) for o in operands} != {str(a), str(b)}:
             raise UnsupportedByTemplates("scan: only sums are scanned by the row template")
         self._has_scan = True
-        out = self.cse.generate(self.compute, f"c.scan_sum({values[0]})", dtype=torch.float32)
+        if is_int:      # exact 64-bit sums
+            out = self.cse.generate(self.compute, f"c.scan_sum_int({values[0]})", dtype=torch.int64)
+        else:
+            out = self.cse.generate(self.compute, f"c.scan_sum({values[0]})", dtype=torch.float32)
         return (out,)
 
     # ------------------------------------------------------------------ reductions

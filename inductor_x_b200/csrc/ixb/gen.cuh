@@ -732,6 +732,51 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     return out;
   }
 
+  // the same scan with exact 64-bit integer sums (cumsum of integer, index or boolean rows)
+  template <class A> __device__ __forceinline__ vi<kE> scan_sum_int(const A& val) {
+    vi<kE> out;
+    long long carry = 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long run = 0;
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j) {
+        run += inside(i, j) ? Cast<long long>::from(at(val, i * Base::kVec + j)) : 0LL;
+        out.v[i * Base::kVec + j] = run;
+      }
+      long long incl = run;
+      const int wl = this->lane & (kGroup - 1);
+#pragma unroll
+      for (int off = 1; off < kGroup; off <<= 1) {
+        const long long up = __shfl_up_sync(kFull, incl, off, kGroup);
+        if (wl >= off) incl += up;
+      }
+      long long before = incl - run;
+      long long total = __shfl_sync(kFull, incl, kGroup - 1, kGroup);
+      if constexpr (TEAM > 32) {
+        long long* slot = reinterpret_cast<long long*>(slot_base());
+        const int w = this->lane >> 5;
+        if ((this->lane & 31) == 31) slot[w * 2] = incl;
+        team_barrier(this->team + 1, TEAM);
+        long long ahead = 0, all = 0;
+#pragma unroll
+        for (int k = 0; k < kW; ++k) {
+          const long long tk = slot[k * 2];
+          if (k < w) ahead += tk;
+          all += tk;
+        }
+        before += ahead;
+        total = all;
+        this->phase ^= 1;
+      }
+      const long long base = carry + before;
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] += base;
+      carry += total;
+    }
+    return out;
+  }
+
   // ---- thread-local folds -------------------------------------------------------------------
   template <class A> __device__ __forceinline__ float local_sum(const A& val) const {
     if constexpr (FULL && op::is_fvec<A>::value) {

@@ -10,7 +10,7 @@ What changed underneath.  The reference whitelists ~50 aten ops (``GENERATE_LIST
 ``pow``, ``sin/cos`` and ``index_select`` break fusion.  Here the templates instantiate any
 pointwise / reduction / indexing body, so the policy is inverted: only the op families no
 template exists for (sorts, random numbers, scatter with a reduction other than add, and every
-scan except a floating ``cumsum`` along the last axis, which the row template scans on chip)
+scan except a ``cumsum`` along the last axis, which the row template scans on chip)
 are forced to extern kernels; accumulating scatters (``index_put(accumulate=True)``,
 ``scatter_add``, ``index_add``) are generated with atomic adds.  The reference's special lowerings are not carried over where they encode
 bugs or NPU workarounds: ``sum_`` always returning fp32 (``:204-215``), the hard-coded
@@ -75,14 +75,21 @@ MAX_SCAN_ROW = 16384
 
 
 def _row_scan_ok(x, axis, dtype) -> bool:
-    """cumsum cases the row template scans: a floating sum along the last axis of a row that a
-    team holds on chip.  Everything else - other axes (the MoE gating graph scans along the
-    token axis), integer inputs, very long or dynamic rows - stays an extern kernel, which is
+    """cumsum cases the row template scans: a floating sum (fp32 accumulation) or an exact
+    64-bit integer sum along the last axis of a row that a team holds on chip.  Everything else
+    - other axes (the MoE gating graph scans along the token axis), a requested output dtype
+    other than the natural one, very long or dynamic rows - stays an extern kernel, which is
     all the reference does for cumsum (``inductor_x/lowering.py:235-245``)."""
     size = x.get_size()
-    if len(size) == 0 or x.get_dtype() not in (torch.float32, torch.float16, torch.bfloat16):
+    if len(size) == 0:
         return False
-    if dtype is not None and dtype != x.get_dtype():
+    if x.get_dtype() in (torch.float32, torch.float16, torch.bfloat16):
+        if dtype is not None and dtype != x.get_dtype():
+            return False
+    elif x.get_dtype() in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.bool):
+        if dtype not in (None, torch.int64):      # integer rows are summed exactly in 64 bits
+            return False
+    else:
         return False
     if axis is None or axis % len(size) != len(size) - 1:
         return False

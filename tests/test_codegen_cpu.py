@@ -259,7 +259,7 @@ def test_short_rows_of_a_whole_line_walk_the_output_digit_first(dry_backend):
 
 def test_cumsum_over_the_last_axis_is_scanned_by_the_row_template(dry_backend):
     """A floating cumsum along the stride-1 axis becomes a row kernel with a team-wide prefix
-    sum (fused with the pointwise work around it); other axes and integer inputs stay extern
+    sum (fused with the pointwise work around it); other axes and other output dtypes stay extern
     kernels, which is all the reference does for cumsum (inductor_x/lowering.py:235-245)."""
     x = torch.randn(64, 1024)
     code = generated(lambda t: torch.cumsum(t * 2.0, -1) + 1.0, x)
@@ -268,5 +268,8 @@ def test_cumsum_over_the_last_axis_is_scanned_by_the_row_template(dry_backend):
     assert extern not in code
     code = generated(lambda t: torch.cumsum(t, 0), x)
     assert "c.scan_sum(" not in code and extern in code
+    # integer rows are summed exactly in 64 bits
     code = generated(lambda t: torch.cumsum(t, -1), torch.arange(64 * 128).reshape(64, 128))
-    assert "c.scan_sum(" not in code and extern in code
+    assert "c.scan_sum_int(" in code and extern not in code
+    code = generated(lambda t: torch.cumsum(t, -1, dtype=torch.float64), x)
+    assert "c.scan_sum" not in code and extern in code

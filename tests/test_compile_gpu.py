@@ -599,3 +599,21 @@ def test_cumsum_along_other_axes_stays_extern(cuda):
     got, code = compile_and_code(lambda t: torch.cumsum(t, 0) * 2.0, x)
     assert "torch.ops.aten.cumsum.default(" in code and "c.scan_sum(" not in code
     torch.testing.assert_close(got, torch.cumsum(x, 0) * 2.0, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32, torch.bool])
+@pytest.mark.parametrize("shape", [(33, 1000), (4, 8192), (129, 24)])
+def test_integer_cumsum_over_the_last_axis_is_exact(cuda, dtype, shape):
+    """Integer, index and boolean rows are scanned with 64-bit sums: bit-exact, including
+    values far above 2^24 (where an fp32 accumulator would round)."""
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    if dtype == torch.bool:
+        x = torch.rand(*shape, generator=g) > 0.5
+    elif dtype == torch.int32:
+        x = torch.randint(-(2 ** 30), 2 ** 30, shape, generator=g, dtype=torch.int32)
+    else:
+        x = torch.randint(-(2 ** 40), 2 ** 40, shape, generator=g, dtype=torch.int64)
+    got, code = compile_and_code(lambda t: torch.cumsum(t, -1), x.to(cuda))
+    assert "c.scan_sum_int(" in code and "torch.ops.aten.cumsum.default(" not in code
+    want = torch.cumsum(x, -1)
+    assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
