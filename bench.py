@@ -676,6 +676,50 @@ class CpMerge(Workload):
         return fn, self.algorithmic_bytes(), "full workload, eager PyTorch on CPU (the reference's forward_update)"
 
 
+class RowCumsum(Workload):
+    """cumsum along the last axis of x[16384, 4096] bf16: the row template's team-wide prefix sum
+    (the reference leaves every cumsum to an extern kernel, inductor_x/lowering.py:235-245)."""
+
+    name = "cumsum_lastdim_bf16_16384x4096"
+    dtype = "bf16"
+    rows, cols = 16384, 4096
+
+    def algorithmic_bytes(self):
+        return 2 * self.rows * self.cols * 2
+
+    def load_host(self, seed):
+        g = torch.Generator().manual_seed(seed)
+        self.host = torch.randn(self.rows, self.cols, generator=g).bfloat16()
+        return self.host
+
+    def setup(self, device, seed, n_sets=3):
+        x = self.load_host(seed).to(device)
+        self.xs = [x] + [x.clone() for _ in range(n_sets - 1)]
+
+    def args(self, i):
+        return (self.xs[i % len(self.xs)],)
+
+    def graph(self):
+        return lambda t: torch.cumsum(t, -1)
+
+    def prebuilt(self, x):
+        raise SystemExit("the scan exists only in generated form")
+
+    def e2e_setup(self, device):
+        self.h_x = self.host.pin_memory()
+        self.d_x = torch.empty_like(self.xs[0])
+        self.h_o = torch.empty_like(self.h_x).pin_memory()
+
+    def e2e_step(self):
+        self.d_x.copy_(self.h_x, non_blocking=True)
+        self.h_o.copy_(self.op(self.d_x), non_blocking=True)
+        return self.h_x.numel() * 2, self.h_o.numel() * 2
+
+    def cpu_sample(self, rows=1024):
+        x = self.host[:rows].float()
+        return (lambda: torch.cumsum(x, -1)), 2 * rows * self.cols * 2, f"{rows} of {self.rows} rows, torch.cumsum on CPU"
+
+
 class PermutedPointwise(Workload):
     """x[8,8,512,128] fp16 -> (x.permute(0,2,1,3) + 1).contiguous(): a permuted pointwise copy whose
     innermost axis is kept (128-bit access on both sides).  64 copies of the tensor per step
@@ -741,9 +785,10 @@ WORKLOADS = {
     "c2": SoftmaxLayerNorm, "c1": AffineGeluRowSum, "c3a_amax": PermutedAmax,
     "c3a_sum": PermutedSum, "c3b": IndexSelect, "c4": FusedAttention, "c4_train": FusedAttentionTraining,
     "c5": LlamaLayer, "cp": CpMerge, "perm": PermutedPointwise, "transpose": TransposedPointwise,
+    "cumsum": RowCumsum,
 }
 #: configurations reported under `configs` after the headline: (key, steps per replay, replays floor)
-SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "perm", "transpose", "c4", "c4_train", "c5")
+SECONDARY = ("c1", "c3a_amax", "c3a_sum", "c3b", "perm", "transpose", "cumsum", "c4", "c4_train", "c5")
 
 
 # ---------------------------------------------------------------------------- driver
@@ -1164,7 +1209,7 @@ def main():
                 try:
                     steps = {"c4": 4, "c4_train": 2, "c5": 3}.get(key, 40)
                     configs.append(run_config(env, key, args,
-                                              args.path if key not in ("c5", "perm", "transpose") else "compiled",
+                                              args.path if key not in ("c5", "perm", "transpose", "cumsum") else "compiled",
                                               steps=steps, min_seconds=0.3, e2e_steps=2))
                 except Exception as e:      # one configuration failing must not lose the line
                     configs.append({"workload": key, "error": f"{type(e).__name__}: {e}"[:300]})
