@@ -108,7 +108,8 @@ def _install_cumsum_lowering():
         return
     extern = lowering.fallback_handler(op, add_to_fallback_set=False)
 
-    def cumsum(x, axis=None, *, dtype=None):
+    def cumsum(x, axis=None, *, dim=None, dtype=None):
+        axis = dim if axis is None else axis      # aten names the argument `dim`
         if _row_scan_ok(x, axis, dtype):
             return stock(x, axis, dtype=dtype)
         return extern(x, axis, dtype=dtype)
