@@ -71,7 +71,7 @@ class Report:
 
     def format(self, side: str = "both") -> str:
         """One ``<side>:<node>:<md5>`` line per node, the shape of the reference's logs
-        (``fx_graph_gen.py:63,80``), followed by the verdict."""
+        (``fx_graph_gen.py:63,80``), followed by the overall result."""
         lines = []
         for r in self.records:
             if side in ("eager", "both"):

@@ -16,7 +16,7 @@ Both are answered on the expression expanded back to the root index variables.  
 vector questions are decided structurally (``vector_access``): the expression must be a sum
 of integer multiples of ``root``, ``ModularIndexing(root, d, m)`` and ``FloorDiv(root, d)``
 whose break points all fall on vector boundaries, which makes it affine inside every
-aligned vector; exact evaluation at sample points then cross-checks the verdict.
+aligned vector; exact evaluation at sample points then cross-checks that decision.
 """
 from __future__ import annotations
 
