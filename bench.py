@@ -432,6 +432,7 @@ class FusedAttention(Workload):
         from oracle import inputs
 
         self.host = inputs.c4(self.B, self.H, self.S, self.D, seed=seed)
+        self.scale = self.host["scale"]
         return self.host
 
     def setup(self, device, seed, n_sets=1):
