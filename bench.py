@@ -678,7 +678,7 @@ class CpMerge(Workload):
 
 
 class RowCumsum(Workload):
-    """cumsum along the last axis of x[16384, 4096] bf16: the row template's team-wide prefix sum
+    """cumsum along the last axis of x[16384, 4096] bf16: the row template's team-wide prefix scan
     (the reference leaves every cumsum to an extern kernel, inductor_x/lowering.py:235-245)."""
 
     name = "cumsum_lastdim_bf16_16384x4096"

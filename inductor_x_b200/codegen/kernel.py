@@ -546,10 +546,10 @@ class B200Kernel(SIMDKernel):
 
     # ------------------------------------------------------------------ scans
     def scan(self, dtypes, combine_fn, values):
-        """Inclusive prefix sum along a stride-1 row held by a team (``cumsum`` over the last
-        axis; the reference keeps it an extern kernel, ``inductor_x/lowering.py:235-245``).
-        Other combine functions, several values, looped or strided rows are refused; the
-        lowering only sends the supported form here."""
+        """Inclusive prefix sum / product along a stride-1 row held by a team (``cumsum`` and
+        ``cumprod`` over the last axis; the reference keeps them extern kernels,
+        ``inductor_x/lowering.py:235-245``).  Other combine functions, several values, looped or
+        strided rows are refused; the lowering only sends the supported form here."""
         assert self.inside_reduction and self.is_row
         if len(values) != 1 or self.looped or self._is_dynamic("r0_"):
             raise UnsupportedByTemplates("scan: one value over a static row held on chip only")
@@ -567,14 +567,21 @@ class B200Kernel(SIMDKernel):
             (res,) = combine_fn((a,), (b,))
         finally:
             self.compute = saved
-        operands = self.op_of(res, "add")
-        if operands is None or {str(o) for o in operands} != {str(a), str(b)}:
-            raise UnsupportedByTemplates("scan: only sums are scanned by the row template")
+        which = None
+        for name in ("add", "mul"):
+            operands = self.op_of(res, name)
+            if operands is not None and {str(o) for o in operands} == {str(a), str(b)}:
+                which = name
+        if which is None:
+            raise UnsupportedByTemplates("scan: only sums and products are scanned by the row template")
         self._has_scan = True
-        if is_int:      # exact 64-bit sums
-            out = self.cse.generate(self.compute, f"c.scan_sum_int({values[0]})", dtype=torch.int64)
+        if is_int:      # exact 64-bit integers
+            iop = "ISum" if which == "add" else "IProd"
+            out = self.cse.generate(self.compute, f"c.template scan_int<typename Ctx::{iop}>({values[0]})",
+                                    dtype=torch.int64)
         else:
-            out = self.cse.generate(self.compute, f"c.scan_sum({values[0]})", dtype=torch.float32)
+            op = "ixb::SumOp" if which == "add" else "ixb::ProdOp"
+            out = self.cse.generate(self.compute, f"c.template scan<{op}>({values[0]})", dtype=torch.float32)
         return (out,)
 
     # ------------------------------------------------------------------ reductions

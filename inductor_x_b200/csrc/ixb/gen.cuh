@@ -682,97 +682,107 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     }
   }
 
-  // ---- inclusive prefix sum along the row (cumsum over the stride-1 axis) ----------------------
+  // ---- inclusive prefix scan along the row (cumsum / cumprod over the stride-1 axis) -----------
   // Row order: vector i of thread t is vector i * TEAM + t of the row.  Per round i every
   // thread scans its own vector, the vector totals are scanned over the team in thread order
   // (shuffles inside a warp, one slot per warp across warps), and the total of the rounds
-  // before is carried along.  fp32 accumulation, as the reference's sums.
-  template <class A> __device__ __forceinline__ vf<kE> scan_sum(const A& val) {
+  // before is carried along.  Op is SumOp or ProdOp; fp32 accumulation, as the reference's sums.
+  template <class Op, class A> __device__ __forceinline__ vf<kE> scan(const A& val) {
     vf<kE> out;
-    float carry = 0.f;
+    float carry = Op::identity();
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      float run = 0.f;
+      float run = Op::identity();
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j) {
-        run += inside(i, j) ? Cast<float>::from(at(val, i * Base::kVec + j)) : 0.f;
+        run = Op::combine(run, inside(i, j) ? Cast<float>::from(at(val, i * Base::kVec + j)) : Op::identity());
         out.v[i * Base::kVec + j] = run;
       }
-      // inclusive scan of `run` over the lanes of this thread's warp (or lane group)
-      float incl = run;
+      // inclusive scan of `run` over the lanes of this thread's warp (or lane group), and the
+      // exclusive one beside it (the operator need not have an inverse)
+      float incl = run, before = Op::identity();
       const int wl = this->lane & (kGroup - 1);
 #pragma unroll
       for (int off = 1; off < kGroup; off <<= 1) {
-        const float up = __shfl_up_sync(kFull, incl, off, kGroup);
-        if (wl >= off) incl += up;
+        const float up_i = __shfl_up_sync(kFull, incl, off, kGroup);
+        if (wl >= off) incl = Op::combine(up_i, incl);
       }
-      float before = incl - run;                                  // lanes ahead of this one
+      if constexpr (std::is_same<Op, SumOp>::value) {
+        before = incl - run;              // sums have an inverse: no second shuffle
+      } else {
+        const float up = __shfl_up_sync(kFull, incl, 1, kGroup);
+        if (wl >= 1) before = up;
+      }
       float total = __shfl_sync(kFull, incl, kGroup - 1, kGroup);  // the warp's (group's) total
       if constexpr (TEAM > 32) {
         float* slot = slot_base();
         const int w = this->lane >> 5;
         if ((this->lane & 31) == 31) slot[w * 4] = incl;
         team_barrier(this->team + 1, TEAM);
-        float ahead = 0.f, all = 0.f;
+        float ahead = Op::identity(), all = Op::identity();
 #pragma unroll
         for (int k = 0; k < kW; ++k) {
           const float tk = slot[k * 4];
-          if (k < w) ahead += tk;
-          all += tk;
+          if (k < w) ahead = Op::combine(ahead, tk);
+          all = Op::combine(all, tk);
         }
-        before += ahead;
+        before = Op::combine(ahead, before);
         total = all;
         this->phase ^= 1;
       }
-      const float base = carry + before;
+      const float base = Op::combine(carry, before);
 #pragma unroll
-      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] += base;
-      carry += total;
+      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] = Op::combine(base, out.v[i * Base::kVec + j]);
+      carry = Op::combine(carry, total);
     }
     return out;
   }
-
-  // the same scan with exact 64-bit integer sums (cumsum of integer, index or boolean rows)
-  template <class A> __device__ __forceinline__ vi<kE> scan_sum_int(const A& val) {
+  // the same scan with exact 64-bit integers (cumsum / cumprod of integer, index or boolean rows)
+  template <class IOp, class A> __device__ __forceinline__ vi<kE> scan_int(const A& val) {
     vi<kE> out;
-    long long carry = 0;
+    long long carry = IOp::id();
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      long long run = 0;
+      long long run = IOp::id();
 #pragma unroll
       for (int j = 0; j < Base::kVec; ++j) {
-        run += inside(i, j) ? Cast<long long>::from(at(val, i * Base::kVec + j)) : 0LL;
+        run = IOp::f(run, inside(i, j) ? Cast<long long>::from(at(val, i * Base::kVec + j)) : IOp::id());
         out.v[i * Base::kVec + j] = run;
       }
-      long long incl = run;
+      long long incl = run, before = IOp::id();
       const int wl = this->lane & (kGroup - 1);
 #pragma unroll
       for (int off = 1; off < kGroup; off <<= 1) {
-        const long long up = __shfl_up_sync(kFull, incl, off, kGroup);
-        if (wl >= off) incl += up;
+        const long long up_i = __shfl_up_sync(kFull, incl, off, kGroup);
+        if (wl >= off) incl = IOp::f(up_i, incl);
       }
-      long long before = incl - run;
+      if constexpr (std::is_same<IOp, ISum>::value) {
+        before = incl - run;
+      } else {
+        const long long up = __shfl_up_sync(kFull, incl, 1, kGroup);
+        if (wl >= 1) before = up;
+      }
       long long total = __shfl_sync(kFull, incl, kGroup - 1, kGroup);
       if constexpr (TEAM > 32) {
         long long* slot = reinterpret_cast<long long*>(slot_base());
         const int w = this->lane >> 5;
         if ((this->lane & 31) == 31) slot[w * 2] = incl;
         team_barrier(this->team + 1, TEAM);
-        long long ahead = 0, all = 0;
+        long long ahead = IOp::id(), all = IOp::id();
 #pragma unroll
         for (int k = 0; k < kW; ++k) {
           const long long tk = slot[k * 2];
-          if (k < w) ahead += tk;
-          all += tk;
+          if (k < w) ahead = IOp::f(ahead, tk);
+          all = IOp::f(all, tk);
         }
-        before += ahead;
+        before = IOp::f(ahead, before);
         total = all;
         this->phase ^= 1;
       }
-      const long long base = carry + before;
+      const long long base = IOp::f(carry, before);
 #pragma unroll
-      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] += base;
-      carry += total;
+      for (int j = 0; j < Base::kVec; ++j) out.v[i * Base::kVec + j] = IOp::f(base, out.v[i * Base::kVec + j]);
+      carry = IOp::f(carry, total);
     }
     return out;
   }

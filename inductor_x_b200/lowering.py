@@ -10,7 +10,7 @@ What changed underneath.  The reference whitelists ~50 aten ops (``GENERATE_LIST
 ``pow``, ``sin/cos`` and ``index_select`` break fusion.  Here the templates instantiate any
 pointwise / reduction / indexing body, so the policy is inverted: only the op families no
 template exists for (sorts, random numbers, scatter with a reduction other than add, and every
-scan except a ``cumsum`` along the last axis, which the row template scans on chip)
+scan except a ``cumsum`` / ``cumprod`` along the last axis, which the row template scans on chip)
 are forced to extern kernels; accumulating scatters (``index_put(accumulate=True)``,
 ``scatter_add``, ``index_add``) are generated with atomic adds.  The reference's special lowerings are not carried over where they encode
 bugs or NPU workarounds: ``sum_`` always returning fp32 (``:204-215``), the hard-coded
@@ -31,7 +31,7 @@ prims = torch.ops.prims
 
 # op families without a B200 template: they stay extern (ATen) kernels
 FALLBACK_LIST = [
-    aten.cumprod, aten.cummax, aten.cummin, aten.logcumsumexp,
+    aten.cummax, aten.cummin, aten.logcumsumexp,
     aten.sort, aten.topk, aten.scatter_reduce, aten.bernoulli, aten.rand, aten.randn, aten.randint, aten.randperm,
     aten.native_dropout, aten.multinomial, aten.bucketize, aten.searchsorted, aten.histc,
 ]
@@ -75,7 +75,7 @@ MAX_SCAN_ROW = 16384
 
 
 def _row_scan_ok(x, axis, dtype) -> bool:
-    """cumsum cases the row template scans: a floating sum (fp32 accumulation) or an exact
+    """cumsum / cumprod cases the row template scans: a floating sum (fp32 accumulation) or an exact
     64-bit integer sum along the last axis of a row that a team holds on chip.  Everything else
     - other axes (the MoE gating graph scans along the token axis), a requested output dtype
     other than the natural one, very long or dynamic rows - stays an extern kernel, which is
@@ -100,28 +100,28 @@ def _row_scan_ok(x, axis, dtype) -> bool:
     return 2 <= n <= MAX_SCAN_ROW
 
 
-def _install_cumsum_lowering():
-    """Stock scan lowering for the supported form, extern kernel otherwise."""
-    op = aten.cumsum.default
-    stock = lowerings.get(op)
-    if stock is None or getattr(stock, "_ixb_guarded", False):
-        return
-    extern = lowering.fallback_handler(op, add_to_fallback_set=False)
+def _install_scan_lowerings():
+    """Stock scan lowering for the supported form of cumsum / cumprod, extern kernel otherwise."""
+    for op in (aten.cumsum.default, aten.cumprod.default):
+        stock = lowerings.get(op)
+        if stock is None or getattr(stock, "_ixb_guarded", False):
+            continue
+        extern = lowering.fallback_handler(op, add_to_fallback_set=False)
 
-    def cumsum(x, axis=None, *, dim=None, dtype=None):
-        axis = dim if axis is None else axis      # aten names the argument `dim`
-        if _row_scan_ok(x, axis, dtype):
-            return stock(x, axis, dtype=dtype)
-        return extern(x, axis, dtype=dtype)
+        def guarded(x, axis=None, *, dim=None, dtype=None, _stock=stock, _extern=extern):
+            axis = dim if axis is None else axis      # aten names the argument `dim`
+            if _row_scan_ok(x, axis, dtype):
+                return _stock(x, axis, dtype=dtype)
+            return _extern(x, axis, dtype=dtype)
 
-    cumsum._ixb_guarded = True
-    lowerings[op] = cumsum
+        guarded._ixb_guarded = True
+        lowerings[op] = guarded
 
 
 def _register_b200_inductor_fallbacks():
     """Force the op families in ``FALLBACK_LIST`` to extern kernels.  Returns the overloads
     that were switched."""
-    _install_cumsum_lowering()
+    _install_scan_lowerings()
     targets = set()
     _init_set(FALLBACK_LIST, targets)
     switched = []

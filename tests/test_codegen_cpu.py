@@ -263,13 +263,18 @@ def test_cumsum_over_the_last_axis_is_scanned_by_the_row_template(dry_backend):
     kernels, which is all the reference does for cumsum (inductor_x/lowering.py:235-245)."""
     x = torch.randn(64, 1024)
     code = generated(lambda t: torch.cumsum(t * 2.0, -1) + 1.0, x)
-    assert code.count("ixb_load_kernel('''") == 1 and "c.scan_sum(" in code and "launch_row_gen<" in code
+    assert code.count("ixb_load_kernel('''") == 1 and "c.template scan<ixb::SumOp>(" in code and "launch_row_gen<" in code
     extern = "torch.ops.aten.cumsum.default("
     assert extern not in code
     code = generated(lambda t: torch.cumsum(t, 0), x)
-    assert "c.scan_sum(" not in code and extern in code
+    assert "c.template scan<" not in code and extern in code
     # integer rows are summed exactly in 64 bits
     code = generated(lambda t: torch.cumsum(t, -1), torch.arange(64 * 128).reshape(64, 128))
-    assert "c.scan_sum_int(" in code and extern not in code
+    assert "c.template scan_int<typename Ctx::ISum>(" in code and extern not in code
     code = generated(lambda t: torch.cumsum(t, -1, dtype=torch.float64), x)
-    assert "c.scan_sum" not in code and extern in code
+    assert "c.template scan" not in code and extern in code
+    # cumprod takes the same path with the product operator; cummax stays extern
+    code = generated(lambda t: torch.cumprod(t, -1), x)
+    assert "c.template scan<ixb::ProdOp>(" in code and "torch.ops.aten.cumprod.default(" not in code
+    code = generated(lambda t: torch.cummax(t, -1)[0], x)
+    assert "c.template scan" not in code and "torch.ops.aten.cummax.default(" in code

@@ -587,7 +587,7 @@ def test_cumsum_over_the_last_axis_is_scanned_on_chip(cuda, dtype, shape):
     x = torch.randn(*shape, generator=g).to(dtype)
     fn = lambda t: torch.cumsum(t * 0.5, -1) + 1.0
     got, code = compile_and_code(fn, x.to(cuda))
-    assert code.count("ixb_load_kernel('''") == 1 and "c.scan_sum(" in code
+    assert code.count("ixb_load_kernel('''") == 1 and "c.template scan<ixb::SumOp>(" in code
     assert "torch.ops.aten.cumsum.default(" not in code
     want = torch.cumsum(x.double() * 0.5, -1) + 1.0
     assert got.dtype == dtype
@@ -597,7 +597,7 @@ def test_cumsum_over_the_last_axis_is_scanned_on_chip(cuda, dtype, shape):
 def test_cumsum_along_other_axes_stays_extern(cuda):
     x = torch.randn(512, 64, device=cuda)
     got, code = compile_and_code(lambda t: torch.cumsum(t, 0) * 2.0, x)
-    assert "torch.ops.aten.cumsum.default(" in code and "c.scan_sum(" not in code
+    assert "torch.ops.aten.cumsum.default(" in code and "c.template scan" not in code
     torch.testing.assert_close(got, torch.cumsum(x, 0) * 2.0, rtol=1e-5, atol=1e-5)
 
 
@@ -614,6 +614,17 @@ def test_integer_cumsum_over_the_last_axis_is_exact(cuda, dtype, shape):
     else:
         x = torch.randint(-(2 ** 40), 2 ** 40, shape, generator=g, dtype=torch.int64)
     got, code = compile_and_code(lambda t: torch.cumsum(t, -1), x.to(cuda))
-    assert "c.scan_sum_int(" in code and "torch.ops.aten.cumsum.default(" not in code
+    assert "c.template scan_int<typename Ctx::ISum>(" in code and "torch.ops.aten.cumsum.default(" not in code
     want = torch.cumsum(x, -1)
     assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("shape", [(64, 1024), (37, 1000), (300, 24)])
+def test_cumprod_over_the_last_axis(cuda, shape):
+    """The same team-wide scan with the product operator (values near 1 so that long rows
+    neither overflow nor vanish); rel 1e-5 against a float64 scan."""
+    g = torch.Generator().manual_seed(sum(shape) + 7)
+    x = 1.0 + 0.01 * torch.randn(*shape, generator=g)
+    got, code = compile_and_code(lambda t: torch.cumprod(t, -1), x.to(cuda))
+    assert "c.template scan<ixb::ProdOp>(" in code and "torch.ops.aten.cumprod.default(" not in code
+    assert graphs.max_rel_err(got.cpu().double(), torch.cumprod(x.double(), -1)) <= 1e-5
