@@ -278,3 +278,24 @@ def test_cumsum_over_the_last_axis_is_scanned_by_the_row_template(dry_backend):
     assert "c.template scan<ixb::ProdOp>(" in code and "torch.ops.aten.cumprod.default(" not in code
     code = generated(lambda t: torch.cummax(t, -1)[0], x)
     assert "c.template scan" not in code and "torch.ops.aten.cummax.default(" in code
+
+
+def test_long_scans_of_few_rows_are_never_cut_into_split_scans(dry_backend, monkeypatch):
+    """Inductor's split heuristic would cut a long scan with few kept rows in two (a decoupled
+    look-back kernel, which only its Triton backend writes); on this backend the row template
+    holds the whole row, so the node stays a plain Scan that fuses like any reduction."""
+    from torch._inductor import ir as inductor_ir
+
+    made = []
+    stock = inductor_ir.SplitScan.__init__
+
+    def spy(self, *a, **k):
+        made.append(1)
+        return stock(self, *a, **k)
+
+    monkeypatch.setattr(inductor_ir.SplitScan, "__init__", spy)
+    for shape in ((1, 16384), (16384,), (2, 16384), (4, 12000)):
+        code = generated(lambda t: torch.cumsum(t, -1).sum(-1), torch.randn(*shape))
+        assert "c.template scan<ixb::SumOp>(" in code and "triton_" not in code
+        assert code.count("ixb_load_kernel(" + "'" * 3) == 1     # the scan and the sum after it: one kernel
+    assert not made

@@ -594,6 +594,20 @@ def test_cumsum_over_the_last_axis_is_scanned_on_chip(cuda, dtype, shape):
     assert graphs.max_rel_err(got.cpu().double(), want) <= graphs.tolerance(dtype)
 
 
+@pytest.mark.parametrize("shape", [(1, 16384), (2, 16384), (4, 12000), (16384,)])
+def test_long_cumsum_of_few_rows_fuses_with_the_reduction_after_it(cuda, shape):
+    """Few kept rows and a long scanned axis: Inductor's heuristic would cut the scan in two;
+    here it stays one row kernel, and the row sum that consumes it joins the same kernel."""
+    g = torch.Generator().manual_seed(sum(shape) + 3)
+    x = torch.randn(*shape, generator=g)
+    got, code = compile_and_code(lambda t: (torch.cumsum(t, -1) * 0.25).sum(-1), x.to(cuda))
+    assert code.count("ixb_load_kernel(" + "'" * 3) == 1 and "c.template scan<ixb::SumOp>(" in code
+    want = (torch.cumsum(x.double(), -1) * 0.25).sum(-1)
+    # the row sum of a running sum cancels heavily: absolute bound scaled by the row's magnitude
+    scale = torch.cumsum(x.double(), -1).abs().sum(-1) * 0.25
+    assert ((got.cpu().double() - want).abs() <= 1e-5 * scale).all()
+
+
 def test_cumsum_along_other_axes_stays_extern(cuda):
     x = torch.randn(512, 64, device=cuda)
     got, code = compile_and_code(lambda t: torch.cumsum(t, 0) * 2.0, x)
