@@ -86,6 +86,18 @@ def _enable_online_softmax_pattern():
     post_grad.prepare_softmax_extra_check = extra_check
 
 
+def _route_random_ops_to_aten():
+    """Random numbers come from ATen's generators (``fallback_random``): ``rand`` / ``randn`` /
+    ``randint`` / ``bernoulli`` / ``native_dropout`` stay extern kernels that draw from the same
+    Philox stream as eager mode, so a compiled dropout is bit-identical to the eager one under the
+    same seed.  Inductor's own seed-and-offset generator exists only inside its Triton kernels (the
+    reference inherits it unchanged); the pointwise work around the random tensor is still fused
+    by the templates."""
+    from torch._inductor import config as inductor_config
+
+    inductor_config.fallback_random = True
+
+
 def register():
     """Perform the registrations (idempotent).  Called at import unless IXB_REGISTER=0."""
     global _registered
@@ -98,6 +110,7 @@ def register():
     _inductor_register_device_op_overrides()
     _register_device_interface()
     _enable_online_softmax_pattern()
+    _route_random_ops_to_aten()
     from .codegen.ir import install_num_splits
 
     install_num_splits()

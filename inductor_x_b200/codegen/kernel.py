@@ -67,8 +67,38 @@ class B200CSEVariable(CSEVariable):
     (fused multiply-add, folded scalar factors, reuse of the online-softmax exponentials,
     sums carried by an earlier exchange) look operands up in that table."""
 
+    #: the integer type the value has in the graph (integers are carried in 64 bits whatever
+    #: that type is; ops whose result can leave its range wrap it back), None for other kinds
+    int_type: Optional[torch.dtype] = None
+
     def update_on_args(self, name, args, kwargs):
         V.kernel.note_op(self, name, args, kwargs)
+        self.int_type = graph_int_type(self, name, args, kwargs or {})
+
+
+_COMPARISONS = ("eq", "ne", "lt", "le", "gt", "ge", "isnan", "isinf", "signbit", "logical_and", "logical_or",
+                "logical_xor", "logical_not", "and_", "or_")
+
+
+def graph_int_type(var, name, args, kwargs) -> Optional[torch.dtype]:
+    """Integer type of an op's result as eager mode would compute it: the conversion target,
+    else the promoted type of the integer operands (Python scalars do not take part)."""
+    if getattr(var, "dtype", None) != torch.int64 or name in _COMPARISONS:
+        return None
+    if name in ("to_dtype", "constant", "index_expr"):
+        dt = kwargs.get("dtype", args[1] if len(args) > 1 else None)
+        return dt if dt in INT_DTYPES else None
+    if name in ("bitwise_left_shift", "bitwise_right_shift"):
+        args = args[:1]                     # the result has the type of the shifted value
+    out = None
+    for a in args:
+        if not isinstance(a, CSEVariable) or a.dtype == torch.bool:
+            continue
+        t = getattr(a, "int_type", None) or (a.dtype if a.dtype in INT_DTYPES else None)
+        if t is None:
+            return None
+        out = t if out is None else torch.promote_types(out, t)
+    return out
 
 
 class B200Kernel(SIMDKernel):
@@ -366,6 +396,13 @@ class B200Kernel(SIMDKernel):
                 "(set IXB_FP64_AS_FP32=1 to accept that)")
 
     def load(self, name: str, index: sympy.Expr) -> CSEVariable:
+        out = self._load_value(name, index)
+        dtype = V.graph.get_dtype(name)
+        if dtype in INT_DTYPES and isinstance(out, B200CSEVariable):
+            out.int_type = dtype
+        return out
+
+    def _load_value(self, name: str, index: sympy.Expr) -> CSEVariable:
         var = self.args.input(name)
         index = self.prepare_indexing(index)
         dtype = V.graph.get_dtype(name)

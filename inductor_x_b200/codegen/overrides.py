@@ -118,6 +118,68 @@ def _call(name):
     return staticmethod(fn)
 
 
+# Integers are carried in 64 bits whatever their storage type.  A value that can leave the
+# range of its type (a narrowing conversion, a left shift, the complement of an unsigned byte)
+# is wrapped back, so that what is computed from it next matches the stored value.
+_INT_RANGE = {torch.bool: (1, False), torch.uint8: (8, False), torch.int8: (8, True), torch.int16: (16, True),
+              torch.int32: (32, True), torch.int64: (64, True)}
+
+
+def _fits(src, dst) -> bool:
+    """Whether every value of integer type ``src`` is a value of integer type ``dst``."""
+    if src not in _INT_RANGE or dst not in _INT_RANGE:
+        return False
+    (sb, ss), (db, ds) = _INT_RANGE[src], _INT_RANGE[dst]
+    return src == dst or (sb < db and (ds or not ss))
+
+
+def _wrap(expr: str, dtype) -> str:
+    bits, signed = _INT_RANGE.get(dtype, (64, True))
+    if bits >= 64 or dtype == torch.bool:
+        return expr
+    return f"{OP}wrap_int<{bits}, {'true' if signed else 'false'}>({expr})"
+
+
+def _dtype_of(v):
+    if isinstance(v, bool):
+        return torch.bool
+    if isinstance(v, int):
+        return torch.int64
+    if isinstance(v, float):
+        return torch.float32
+    return getattr(v, "int_type", None) or getattr(v, "dtype", None)
+
+
+def _narrow_int_result(*vals):
+    """The integer type narrower than 64 bits that eager mode gives the result of an
+    arithmetic op on ``vals`` (None when the result is not such an integer)."""
+    out = None
+    for v in vals:
+        if isinstance(v, (bool, int)):
+            continue                       # Python scalars do not take part in the promotion
+        t = _dtype_of(v)
+        if t == torch.bool:
+            continue
+        if t not in INT_DTYPES:
+            return None
+        out = t if out is None else torch.promote_types(out, t)
+    return out if out in _INT_RANGE and _INT_RANGE[out][0] < 64 else None
+
+
+def _bitwise(logical: str, bitwise: str):
+    """and / or / xor: the logical form for booleans, the bit pattern for integers."""
+
+    def fn(a, b):
+        da, db = _dtype_of(a), _dtype_of(b)
+        if da in FLOAT_DTYPES or db in FLOAT_DTYPES:
+            raise NotImplementedError(f"{bitwise} of floating operands")
+        if da in (torch.bool, None) and db in (torch.bool, None):
+            return f"{OP}{logical}({a}, {b})"
+        return f"{OP}{bitwise}({a}, {b})"
+
+    return staticmethod(fn)
+
+
 class B200Overrides(OpOverrides):
     """Text of each pointwise op.  Floating math is fp32 whatever the storage type."""
 
@@ -126,7 +188,10 @@ class B200Overrides(OpOverrides):
         if dtype == torch.bool:
             return f"{OP}to_bool({x})"
         if dtype in INT_DTYPES:
-            return f"{OP}to_int({x})"
+            src = src_dtype if src_dtype is not None else _dtype_of(x)
+            if src in FLOAT_DTYPES or _fits(src, dtype):
+                return f"{OP}to_int({x})"     # (a float outside the range is undefined in eager mode too)
+            return _wrap(f"{OP}to_int({x})", dtype)
         return f"{OP}to_float({x})"
 
     @staticmethod
@@ -169,21 +234,26 @@ class B200Overrides(OpOverrides):
         # the raw handler (not the OpsValue wrapper): callers read .dtype of the result
         return V.ops.where(new_mask, result, other)
 
-    @staticmethod
-    def bitwise_and(a, b):
-        return f"{OP}logical_and({a}, {b})"
-
-    @staticmethod
-    def bitwise_or(a, b):
-        return f"{OP}logical_or({a}, {b})"
-
-    @staticmethod
-    def bitwise_xor(a, b):
-        return f"{OP}logical_xor({a}, {b})"
+    bitwise_and = _bitwise("logical_and", "bit_and")
+    bitwise_or = _bitwise("logical_or", "bit_or")
+    bitwise_xor = _bitwise("logical_xor", "bit_xor")
 
     @staticmethod
     def bitwise_not(a):
-        return f"{OP}logical_not({a})"
+        da = _dtype_of(a)
+        if da in (torch.bool, None):
+            return f"{OP}logical_not({a})"
+        if da in FLOAT_DTYPES:
+            raise NotImplementedError("bitwise_not of a floating operand")
+        return _wrap(f"{OP}bit_not({a})", da if da == torch.uint8 else torch.int64)
+
+    @staticmethod
+    def bitwise_left_shift(a, b):
+        return _wrap(f"{OP}lshift({a}, {b})", _narrow_int_result(a))
+
+    @staticmethod
+    def bitwise_right_shift(a, b):
+        return f"{OP}rshift({a}, {b})"
 
     @staticmethod
     def and_(a, b):
@@ -222,7 +292,7 @@ class _Peephole:
                 m = k.op_of(p, "mul")
                 if m is not None and _floats(k, *m):
                     return f"{OP}fma({m[0]}, {m[1]}, {q})"
-        return f"{OP}add({a}, {b})"
+        return _wrap(f"{OP}add({a}, {b})", _narrow_int_result(a, b))
 
     @staticmethod
     def sub(a, b):
@@ -231,7 +301,7 @@ class _Peephole:
             m = k.op_of(a, "mul")
             if m is not None and _floats(k, *m) and k.is_scalar(b):
                 return f"{OP}fma({m[0]}, {m[1]}, {OP}neg({b}))"
-        return f"{OP}sub({a}, {b})"
+        return _wrap(f"{OP}sub({a}, {b})", _narrow_int_result(a, b))
 
     @staticmethod
     def _gelu(k, a, b):
@@ -277,7 +347,7 @@ class _Peephole:
                 d = k.op_of(p, "truediv")
                 if d is not None and _floats(k, *d) and k.is_scalar(d[1]) and not k.is_scalar(d[0]):
                     return f"{OP}mul({d[0]}, {OP}truediv({q}, {d[1]}))"
-        return f"{OP}mul({a}, {b})"
+        return _wrap(f"{OP}mul({a}, {b})", _narrow_int_result(a, b))
 
     @staticmethod
     def truediv(a, b):
@@ -310,7 +380,8 @@ class _Peephole:
 
 
 for _name in ["exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "rsqrt", "sin", "cos",
-              "tan", "asin", "acos", "atan", "sinh", "cosh", "tanh", "erf", "erfc", "lgamma", "floor",
+              "tan", "asin", "acos", "atan", "sinh", "cosh", "tanh", "asinh", "acosh", "atanh", "erf", "erfc",
+              "erfinv", "nextafter", "ldexp", "lgamma", "floor",
               "ceil", "trunc", "round", "reciprocal", "sigmoid", "abs", "neg", "square", "relu",
               "sign", "isnan", "isinf", "signbit", "truediv", "pow", "fmod", "atan2", "copysign",
               "hypot", "add", "sub", "mul", "maximum", "minimum", "floordiv", "truncdiv",
@@ -319,7 +390,10 @@ for _name in ["exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "
     setattr(B200Overrides, _name, _call(_name))
 for _name in ["add", "sub", "mul", "truediv", "exp"]:
     setattr(B200Overrides, _name, staticmethod(getattr(_Peephole, _name)))
+B200Overrides.neg = staticmethod(lambda a: _wrap(f"{OP}neg({a})", _narrow_int_result(a)))
 B200Overrides.mod = _call("mod")
+B200Overrides.fma = _call("fma")
+B200Overrides.mul_rn = _call("mul")       # a product that is never contracted: its name keeps it out of the fma peephole
 B200Overrides.int_truediv = _call("truediv")
 B200Overrides.libdevice_exp = staticmethod(_Peephole.exp)
 B200Overrides.libdevice_sqrt = _call("sqrt")

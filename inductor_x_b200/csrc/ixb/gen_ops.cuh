@@ -70,6 +70,10 @@ IXB_OP_F1(sinh, sinhf(x))
 IXB_OP_F1(cosh, coshf(x))
 IXB_OP_F1(tanh, tanhf(x))
 IXB_OP_F1(erfc, erfcf(x))
+IXB_OP_F1(asinh, asinhf(x))
+IXB_OP_F1(acosh, acoshf(x))
+IXB_OP_F1(atanh, atanhf(x))
+IXB_OP_F1(erfinv, erfinvf(x))
 IXB_OP_F1(lgamma, lgammaf(x))
 IXB_OP_F1(floor, floorf(x))
 IXB_OP_F1(ceil, ceilf(x))
@@ -261,6 +265,8 @@ IXB_OP_F2(fmod, fmodf(x, y))
 IXB_OP_F2(atan2, atan2f(x, y))
 IXB_OP_F2(copysign, copysignf(x, y))
 IXB_OP_F2(hypot, hypotf(x, y))
+IXB_OP_F2(nextafter, nextafterf(x, y))
+IXB_OP_F2(ldexp, ldexpf(x, (int)y))
 #undef IXB_OP_F2
 
 // kind-preserving binary ops (int with int stays int); max/min propagate NaN like torch
@@ -327,6 +333,40 @@ IXB_OP_B2(logical_xor, x != y)
 #undef IXB_OP_B2
 template <class A> __device__ __forceinline__ typename bres<rank<A>::n>::type logical_not(const A& a) {
   return map1<typename bres<rank<A>::n>::type>([](bool x) { return !x; }, a);
+}
+
+// bitwise ops of integer operands (booleans take the logical forms above).  Integers are held
+// sign-extended (unsigned bytes zero-extended) in 64 bits, so and / or / xor / not of two
+// values of one type give that type's result in the same representation; a shift count outside
+// [0, 63] gives 0 (left) or the sign fill (right).
+#define IXB_OP_I2(NAME, EXPR)                                                                  \
+  template <class A, class B>                                                                  \
+  __device__ __forceinline__ typename ires<rank2<A, B>::n>::type NAME(const A& a, const B& b) { \
+    return map2<typename ires<rank2<A, B>::n>::type>(                                          \
+        [](long long x, long long y) { return (long long)(EXPR); }, a, b);                     \
+  }
+IXB_OP_I2(bit_and, x & y)
+IXB_OP_I2(bit_or, x | y)
+IXB_OP_I2(bit_xor, x ^ y)
+IXB_OP_I2(lshift, ((unsigned long long)y > 63ULL ? 0LL : (long long)((unsigned long long)x << y)))
+IXB_OP_I2(rshift, (x >> ((unsigned long long)y > 63ULL ? 63 : y)))
+#undef IXB_OP_I2
+template <class A> __device__ __forceinline__ typename ires<rank<A>::n>::type bit_not(const A& a) {
+  return map1<typename ires<rank<A>::n>::type>([](long long x) { return ~x; }, a);
+}
+// the value an integer of BITS bits (signed or not) holds after a conversion or an operation
+// that can leave its range: two's-complement wrap, back in the 64-bit representation
+template <int BITS, bool SIGNED, class A>
+__device__ __forceinline__ typename ires<rank<A>::n>::type wrap_int(const A& a) {
+  return map1<typename ires<rank<A>::n>::type>(
+      [](long long x) {
+        if constexpr (BITS == 8 && SIGNED) return (long long)(signed char)x;
+        else if constexpr (BITS == 8) return (long long)(unsigned char)x;
+        else if constexpr (BITS == 16) return (long long)(short)x;
+        else if constexpr (BITS == 32) return (long long)(int)x;
+        else return x;
+      },
+      a);
 }
 
 #define IXB_OP_CMP(NAME, OP)                                                                   \

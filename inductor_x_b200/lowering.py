@@ -37,6 +37,24 @@ FALLBACK_LIST = [
 ]
 
 
+def _special_function_ops():
+    """The special functions Inductor's Triton and C++ backends carry their own
+    implementations of (Bessel and gamma families, orthogonal polynomials, ``digamma``,
+    ``zeta``, ``ndtri`` ...): no template implements them, so they stay extern kernels."""
+    from torch._inductor.codegen.common import pointwise_overrides_data
+
+    out = []
+    for name, data in pointwise_overrides_data.items():
+        if name in ("fma", "mul_rn"):
+            continue
+        for ns in (aten, prims):
+            op = getattr(ns, data.name, None)
+            if op is not None:
+                out.append(op)
+    out.append(aten.frexp)
+    return out
+
+
 def make_reduction(reduction_type: str, override_return_dtype=None):
     """``Reduction.create`` wrapper that records which axes a reduction keeps and reduces
     on the IR node (``kept_idx`` / ``reduced_idx``) and realises it, as
@@ -116,6 +134,16 @@ def _install_scan_lowerings():
 
         guarded._ixb_guarded = True
         lowerings[op] = guarded
+    # scans with other operators (running maximum / minimum with their indices, log-sum-exp):
+    # their stock lowerings build a Scan node whenever the backend declares scans, so they are
+    # pinned to the extern kernel here
+    for op in (aten.logcumsumexp.default, aten.cummax.default, aten.cummin.default):
+        stock = lowerings.get(op)
+        if stock is None or getattr(stock, "_ixb_guarded", False):
+            continue
+        extern = lowering.fallback_handler(op, add_to_fallback_set=False)
+        extern._ixb_guarded = True
+        lowerings[op] = extern
 
 
 def _register_b200_inductor_fallbacks():
@@ -123,7 +151,7 @@ def _register_b200_inductor_fallbacks():
     that were switched."""
     _install_scan_lowerings()
     targets = set()
-    _init_set(FALLBACK_LIST, targets)
+    _init_set(FALLBACK_LIST + _special_function_ops(), targets)
     switched = []
     for op in targets:
         if isinstance(op, torch._ops.OpOverloadPacket):

@@ -24,15 +24,20 @@ def _dry_cpu_backend(candidates: bool):
 
     init_backend_registration()
     old = (get_scheduling_for_device("cpu"), get_wrapper_codegen_for_device("cpu"))
-    saved = (config.dry_run, config.prebuild_candidates, torch._inductor.config.fx_graph_cache)
+    saved = (config.dry_run, config.prebuild_candidates, torch._inductor.config.fx_graph_cache,
+             torch._inductor.config.cpu_backend)
     config.dry_run, config.prebuild_candidates = True, candidates
     torch._inductor.config.fx_graph_cache = False
+    # the op handlers ask which backend family is current (it decides how the result type of a
+    # masked sub-block is found): answer as on the GPU
+    torch._inductor.config.cpu_backend = "triton"
     register_backend_for_device("cpu", B200Scheduling, B200WrapperCodeGen)
     try:
         yield
     finally:
         register_backend_for_device("cpu", *old)
-        config.dry_run, config.prebuild_candidates, torch._inductor.config.fx_graph_cache = saved
+        (config.dry_run, config.prebuild_candidates, torch._inductor.config.fx_graph_cache,
+         torch._inductor.config.cpu_backend) = saved
 
 
 def prebuild(graphs: Iterable[Tuple[str, Callable, Sequence]], candidates: bool = True, verbose: bool = True):

@@ -17,24 +17,18 @@ pytestmark = pytest.mark.skipif(shutil.which("nvcc") is None, reason="nvcc not a
 
 @pytest.fixture(scope="module")
 def dry_backend(tmp_path_factory):
+    """The backend registered for CPU tensors in dry-run mode: sources are emitted and built
+    with nvcc exactly as on a GPU, nothing is launched."""
     os.environ["IXB_CACHE_DIR"] = str(tmp_path_factory.mktemp("ixbcache"))
     import inductor_x_b200
     from inductor_x_b200 import config
-    from inductor_x_b200.codegen import B200Scheduling, B200WrapperCodeGen
-    from torch._inductor.codegen.common import (get_scheduling_for_device, get_wrapper_codegen_for_device,
-                                                register_backend_for_device)
+    from inductor_x_b200.prebuild import _dry_cpu_backend
 
-    config.dry_run = True
+    old_dir = config.cache_dir
     config.cache_dir = os.environ["IXB_CACHE_DIR"]
-    torch._inductor.config.fx_graph_cache = False
-    from torch._inductor.codegen.common import init_backend_registration
-
-    init_backend_registration()
-    old = (get_scheduling_for_device("cpu"), get_wrapper_codegen_for_device("cpu"))
-    register_backend_for_device("cpu", B200Scheduling, B200WrapperCodeGen)
-    yield
-    register_backend_for_device("cpu", *old)
-    config.dry_run = False
+    with _dry_cpu_backend(False):
+        yield
+    config.cache_dir = old_dir
 
 
 def launch_shape(code):
@@ -299,3 +293,57 @@ def test_long_scans_of_few_rows_are_never_cut_into_split_scans(dry_backend, monk
         assert "c.template scan<ixb::SumOp>(" in code and "triton_" not in code
         assert code.count("ixb_load_kernel(" + "'" * 3) == 1     # the scan and the sum after it: one kernel
     assert not made
+
+
+def test_integer_bitwise_ops_keep_the_bit_pattern(dry_backend):
+    """and / or / xor / not print as bit operations for integer operands and as logical ones
+    for booleans; shifts exist; a left shift and the complement of an unsigned byte are wrapped
+    back into the range of their type (integers are carried in 64 bits)."""
+    a, b = torch.randint(1, 100, (1000,)), torch.randint(0, 5, (1000,))
+    code = generated(lambda a, b: ((a & b) | (a ^ 7)) + (~a) + (a << b) + (a >> b), a, b)
+    for name in ("bit_and(", "bit_or(", "bit_xor(", "bit_not(", "lshift(", "rshift("):
+        assert "ixb::gen::op::" + name in code
+    assert "logical_" not in code and "wrap_int" not in code        # 64-bit values need no wrap
+    code = generated(lambda a, b: (a > 3) & (b < 2) | ~(a == b), a, b)
+    assert "logical_and(" in code and "logical_not(" in code and "bit_" not in code
+    code = generated(lambda a, b: (a.to(torch.int32) << b.to(torch.int32)) + 1, a, b)
+    assert "wrap_int<32, true>(ixb::gen::op::lshift(" in code
+    code = generated(lambda a: (~a).float(), a.to(torch.uint8))
+    assert "wrap_int<8, false>(ixb::gen::op::bit_not(" in code
+
+
+def test_narrowing_integer_conversions_wrap(dry_backend):
+    """int64 -> int8 / uint8 / int16 / int32 wraps like the stored value would, and so do sums,
+    differences and products of integers narrower than 64 bits; widening conversions and
+    conversions from floating values are plain."""
+    a = torch.randint(-1000, 1000, (1000,))
+    code = generated(lambda a: a.to(torch.uint8).float() + a.to(torch.int8).float(), a)
+    assert "wrap_int<8, false>(" in code and "wrap_int<8, true>(" in code
+    code = generated(lambda a: a.to(torch.int64) * 3, a.to(torch.int32))
+    assert "wrap_int" not in code
+    code = generated(lambda x: (x * 10).to(torch.int32) + 1, torch.randn(1000))
+    assert "(ixb::gen::op::to_int(" not in code                    # the conversion itself is plain ...
+    assert "wrap_int<32, true>(ixb::gen::op::add(" in code         # ... the int32 sum after it can overflow
+
+
+def test_ops_without_a_template_stay_extern_and_the_rest_compiles(dry_backend):
+    """Random numbers come from ATen's generators (dropout in training mode compiles, the scaling
+    around it is generated); scans with other operators and the special functions Inductor only
+    has in its own backends stay extern kernels; inverse hyperbolic functions, erfinv, ldexp and
+    nextafter are generated; a constant pad (a masked sub-block) is generated."""
+    x = torch.rand(64, 256) * 0.8 + 0.1
+    code = generated(lambda t: F.dropout(t * 2.0, 0.1, True) + 1.0, x)
+    assert "ixb_load_kernel(" in code and ("aten.native_dropout" in code or "aten.bernoulli" in code
+                                           or "aten.rand" in code)
+    code = generated(lambda t: torch.logcumsumexp(t, -1), x)
+    assert "torch.ops.aten.logcumsumexp.default(" in code and "c.template scan" not in code
+    code = generated(lambda t: torch.digamma(t) + torch.special.i0(t), x)
+    assert "torch.ops.aten.digamma.default(" in code and "torch.ops.aten.i0.default(" in code
+    code = generated(lambda t: torch.asinh(t) + torch.acosh(t + 1) + torch.atanh(t) + torch.erfinv(t)
+                     + torch.nextafter(t, t + 1) + torch.ldexp(t, torch.tensor(3)), x)
+    for name in ("asinh(", "acosh(", "atanh(", "erfinv(", "nextafter("):
+        assert "ixb::gen::op::" + name in code
+    assert code.count("ixb_load_kernel(") == 1
+    code = generated(lambda t: F.max_pool2d(F.pad(t, (1, 2, 3, 4), value=-1.0), 3, 2, 1), torch.randn(2, 3, 16, 16))
+    assert code.count("ixb_load_kernel(") == 1 and "= torch.ops.aten.constant_pad_nd.default(" not in code
+    assert "ixb::gen::op::where(" in code                 # the pad value outside the source's bounds

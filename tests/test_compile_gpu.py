@@ -642,3 +642,67 @@ def test_cumprod_over_the_last_axis(cuda, shape):
     got, code = compile_and_code(lambda t: torch.cumprod(t, -1), x.to(cuda))
     assert "c.template scan<ixb::ProdOp>(" in code and "torch.ops.aten.cumprod.default(" not in code
     assert graphs.max_rel_err(got.cpu().double(), torch.cumprod(x.double(), -1)) <= 1e-5
+
+
+def test_integer_bit_operations_match_eager(cuda):
+    """Bitwise ops, shifts, narrowing conversions and overflowing sums / products of integers:
+    bit-exact against eager mode (integers are carried in 64 bits and wrapped back where the
+    result can leave the range of its type)."""
+    g = torch.Generator().manual_seed(11)
+    a = torch.randint(-(2 ** 40), 2 ** 40, (5000,), generator=g)
+    b = torch.randint(0, 40, (5000,), generator=g)
+    fn = lambda a, b: ((a & (b * 977)) | (a ^ 0x5555)) + (~a) + (a << b) + (a >> b)
+    got, code = compile_and_code(fn, a.to(cuda), b.to(cuda))
+    assert "ixb::gen::op::bit_and(" in code and "logical_" not in code
+    assert torch.equal(got.cpu(), fn(a, b))
+    a32 = torch.randint(-(2 ** 31), 2 ** 31 - 1, (5000,), generator=g, dtype=torch.int32)
+    b32 = torch.randint(0, 31, (5000,), generator=g, dtype=torch.int32)
+
+    def narrow(a, b):
+        return ((a << b) + a * 1103515245 - b, (~a.to(torch.uint8)).float(),
+                a.to(torch.int8).to(torch.int64) + a.to(torch.int16), (a > 0) ^ (b > 15))
+
+    got, code = compile_and_code(narrow, a32.to(cuda), b32.to(cuda))
+    assert "wrap_int<32, true>(" in code and "wrap_int<8, false>(" in code
+    for o, w in zip(got, narrow(a32, b32)):
+        assert o.dtype == w.dtype and torch.equal(o.cpu(), w)
+
+
+def test_padding_pooling_and_dropout(cuda):
+    """A constant pad feeding a strided max-pool (masked sub-blocks) against eager mode, and a
+    training-mode dropout: the random mask comes from ATen's generator, the scaling around it is
+    generated, the same seed gives the same result."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(2, 3, 33, 31, generator=g)
+    fn = lambda t: F.max_pool2d(F.pad(t, (1, 2, 3, 4), value=-1.0) * 2.0, 3, 2, 1)
+    got, code = compile_and_code(fn, x.to(cuda))
+    assert "= torch.ops.aten.constant_pad_nd.default(" not in code
+    torch.testing.assert_close(got.cpu(), fn(x), rtol=1e-6, atol=1e-6)
+    y = torch.rand(256, 1024, generator=g) + 0.5
+    drop = torch.compile(lambda t: F.dropout(t * 2.0, 0.25, True) + 1.0)
+    torch.manual_seed(5)
+    o1 = drop(y.to(cuda))
+    torch.manual_seed(5)
+    o2 = drop(y.to(cuda))
+    assert torch.equal(o1, o2)
+    kept = o1.cpu() != 1.0
+    assert abs(kept.float().mean().item() - 0.75) < 0.01
+    torch.testing.assert_close(o1.cpu()[kept], (y * 2.0 / 0.75 + 1.0)[kept], rtol=1e-5, atol=1e-5)
+
+
+def test_inverse_hyperbolic_and_extern_special_functions(cuda):
+    """asinh / acosh / atanh / erfinv / nextafter / ldexp are generated (rel 1e-5 against float64);
+    digamma, i0 and logcumsumexp stay extern kernels inside a compiled graph."""
+    g = torch.Generator().manual_seed(13)
+    x = torch.rand(64, 300, generator=g) * 0.8 + 0.1
+    fn = lambda t: (torch.asinh(t) + torch.acosh(t + 1) + torch.atanh(t) + torch.erfinv(t)
+                    + torch.nextafter(t, t + 1) + torch.ldexp(t, torch.tensor(3, device=t.device)))
+    got, code = compile_and_code(fn, x.to(cuda))
+    assert code.count("ixb_load_kernel('''") == 1 and "ixb::gen::op::erfinv(" in code
+    want = (torch.asinh(x.double()) + torch.acosh(x.double() + 1) + torch.atanh(x.double()) + torch.erfinv(x.double())
+            + x.double() + x.double() * 8)
+    assert graphs.max_rel_err(got.cpu().double(), want) <= 1e-5
+    fn = lambda t: torch.logcumsumexp(torch.digamma(t) * 2.0, -1) + torch.special.i0(t)
+    got, code = compile_and_code(fn, x.to(cuda))
+    assert "torch.ops.aten.digamma.default(" in code and "torch.ops.aten.logcumsumexp.default(" in code
+    torch.testing.assert_close(got.cpu(), fn(x), rtol=1e-4, atol=1e-5)
