@@ -306,9 +306,15 @@ IXB_OP_PACKED2(mul, mul2(x, y), x * y, x * y)
 IXB_OP_ARITH2(maximum, MaxOp::combine(x, y), (x > y ? x : y))
 IXB_OP_ARITH2(minimum, MinOp::combine(x, y), (x < y ? x : y))
 // python-style floor division and modulo for integers, C-style truncation for truncdiv
+// floating remainder with the sign of the divisor, from the exact fmod (x - y * floor(x / y)
+// would lose every digit once x / y no longer fits the mantissa)
+__device__ __forceinline__ float py_fmod(float x, float y) {
+  const float r = fmodf(x, y);
+  return (r != 0.f && ((r < 0.f) != (y < 0.f))) ? r + y : r;
+}
 IXB_OP_ARITH2(floordiv, floorf(x / y), ((x / y) - ((x % y != 0) && ((x < 0) != (y < 0)))))
 IXB_OP_ARITH2(truncdiv, truncf(x / y), x / y)
-IXB_OP_ARITH2(remainder, (x - y * floorf(x / y)), ((x % y) + (((x % y) != 0 && ((x % y) < 0) != (y < 0)) ? y : 0)))
+IXB_OP_ARITH2(remainder, py_fmod(x, y), ((x % y) + (((x % y) != 0 && ((x % y) < 0) != (y < 0)) ? y : 0)))
 IXB_OP_ARITH2(mod, fmodf(x, y), x % y)
 #undef IXB_OP_ARITH2
 

@@ -706,3 +706,78 @@ def test_inverse_hyperbolic_and_extern_special_functions(cuda):
     got, code = compile_and_code(fn, x.to(cuda))
     assert "torch.ops.aten.digamma.default(" in code and "torch.ops.aten.logcumsumexp.default(" in code
     torch.testing.assert_close(got.cpu(), fn(x), rtol=1e-4, atol=1e-5)
+
+
+def _zoo_inputs():
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(4099, generator=g) * 3
+    y = torch.randn(4099, generator=g) * 2
+    y[y.abs() < 0.05] = 0.7
+    x[:8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 1e10, -1e10])        # round-half-even, huge ratios
+    i = torch.randint(-50, 50, (4099,), generator=g)
+    j = torch.randint(-7, 8, (4099,), generator=g)
+    j[j == 0] = 3
+    return x, y, i, j
+
+
+def test_floating_pointwise_ops_match_eager(cuda):
+    """One kernel per family of floating pointwise ops (several outputs each) against eager mode on
+    the same inputs: rounding modes, signs of remainder / fmod / floor division, NaN handling of
+    maximum / minimum / clamp / relu, selects, the transcendental set."""
+    x, y, _, _ = _zoo_inputs()
+    xn = x.clone()
+    xn[100:110] = float("nan")
+
+    def rounding(a, b):
+        return (torch.round(a), torch.trunc(a), torch.floor(a), torch.ceil(a), torch.sign(a), torch.remainder(a, b),
+                torch.fmod(a, b), torch.floor_divide(a, b), torch.div(a, b, rounding_mode="trunc"), torch.copysign(a, b))
+
+    def nans(a, b):
+        return (torch.maximum(a, b), torch.minimum(a, b), a.clamp(-1.0, 1.0), torch.relu(a), torch.where(a > b, a, b),
+                torch.isnan(a), torch.nan_to_num(a, nan=2.0), (a != a) | (b > 0), torch.hypot(a, b), torch.atan2(a, b))
+
+    def transcendental(a):
+        p = a.abs() + 0.1
+        return (torch.exp(a * 0.3), torch.expm1(a * 0.1), torch.log(p), torch.log2(p), torch.log10(p), torch.log1p(p),
+                torch.sqrt(p), torch.rsqrt(p), torch.sin(a), torch.cos(a), torch.tan(a.clamp(-1.2, 1.2)), torch.tanh(a),
+                torch.sigmoid(a), torch.erf(a), torch.erfc(a), torch.sinh(a * 0.5), torch.cosh(a * 0.5),
+                torch.atan(a), torch.asin(a.clamp(-1, 1) * 0.99), torch.acos(a.clamp(-1, 1) * 0.99), torch.exp2(a * 0.5),
+                torch.pow(p, 1.7), torch.pow(p, b_const), torch.lgamma(p), torch.reciprocal(p), torch.square(a),
+                F.gelu(a), F.silu(a), F.softplus(a), torch.abs(a), -a)
+
+    b_const = 3
+    for fn, args, tol in ((rounding, (x, y), 1e-6), (nans, (xn, y), 1e-6), (transcendental, (x[8:],), 2e-5)):
+        got, code = compile_and_code(fn, *(a.to(cuda) for a in args))
+        want = fn(*(a.double() if tol > 1e-6 else a for a in args))
+        for k, (o, w) in enumerate(zip(got, want)):
+            assert o.shape == w.shape, (fn.__name__, k)
+            if w.dtype == torch.bool:
+                assert torch.equal(o.cpu(), w), (fn.__name__, k)
+            else:
+                torch.testing.assert_close(o.cpu().double(), w.double(), rtol=tol, atol=tol, equal_nan=True,
+                                           msg=lambda m, k=k: f"{fn.__name__} output {k}: {m}")
+
+
+def test_integer_pointwise_ops_match_eager(cuda):
+    """Integer arithmetic with negative operands (floor division, remainder, truncating division,
+    fmod, abs, sign, min / max, clamp, selects, comparisons, powers, conversions): bit-exact."""
+    x, _, i, j = _zoo_inputs()
+
+    def ints(a, b):
+        return (a // b, a % b, torch.div(a, b, rounding_mode="trunc"), torch.fmod(a, b), a.abs(), torch.sign(a),
+                torch.maximum(a, b), torch.minimum(a, b), a.clamp(-10, 10), torch.where(a > b, a, b), a * b - a,
+                (a >= b) & (a != 3), a ** 2, -a, a / b, (a.float() * 0.37).to(torch.int64), a.to(torch.int16) * 1000,
+                (a + 200).to(torch.uint8) + 100, a.to(torch.bool), (a > 0).to(torch.int32) + a.to(torch.int32))
+
+    got, code = compile_and_code(ints, i.to(cuda), j.to(cuda))
+    for k, (o, w) in enumerate(zip(got, ints(i, j))):
+        assert o.dtype == w.dtype, k
+        if w.dtype.is_floating_point:
+            torch.testing.assert_close(o.cpu(), w, rtol=1e-6, atol=1e-6)
+        else:
+            assert torch.equal(o.cpu(), w), k
+    # float -> int truncates toward zero
+    got, _ = compile_and_code(lambda t: ((t * 3).to(torch.int32), (t * 3).to(torch.int64) // 2), x[8:].to(cuda))
+    want = ((x[8:] * 3).to(torch.int32), (x[8:] * 3).to(torch.int64) // 2)
+    for o, w in zip(got, want):
+        assert torch.equal(o.cpu(), w)
