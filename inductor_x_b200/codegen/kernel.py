@@ -660,7 +660,9 @@ class B200Kernel(SIMDKernel):
             self.online[info["value"]] = info
         elif reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
-            tag = self._placeholder("R", None, f"c.template reduce_arg<{is_max}>({value})", "", outer_ok=False)
+            # 32- and 64-bit integers are compared as integers (a float merges neighbours beyond 2^24)
+            form = "reduce_arg_int" if src_dtype in (torch.int32, torch.int64) else "reduce_arg"
+            tag = self._placeholder("R", None, f"c.template {form}<{is_max}>({value})", "", outer_ok=False)
             self._reduction_marker(tag)
             result = self.cse.generate(self.compute, tag, dtype=torch.int64)
         elif reduction_type == "any":
@@ -726,9 +728,16 @@ class B200Kernel(SIMDKernel):
             return result
         if reduction_type in ("argmax", "argmin"):
             is_max = "true" if reduction_type == "argmax" else "false"
-            self.body.writeline(f"ixb::ArgPair {acc} = ixb::ArgOp<{is_max}>::identity();")
-            self.compute.writeline(f"{acc} = ixb::ArgOp<{is_max}>::combine({acc}, c.template local_arg<{is_max}>({value}));")
-            text, out_dtype = f"c.template xreduce_arg<{is_max}>({acc})", torch.int64
+            if src_dtype in (torch.int32, torch.int64):
+                self.body.writeline(f"typename Ctx::ArgPairI {acc} = Ctx::template arg_identity_int<{is_max}>();")
+                self.compute.writeline(f"{acc} = Ctx::template arg_better<{is_max}>({acc}, "
+                                       f"c.template local_arg_int<{is_max}>({value}));")
+                text, out_dtype = f"c.template xreduce_arg_int<{is_max}>({acc})", torch.int64
+            else:
+                self.body.writeline(f"ixb::ArgPair {acc} = ixb::ArgOp<{is_max}>::identity();")
+                self.compute.writeline(f"{acc} = ixb::ArgOp<{is_max}>::combine({acc}, "
+                                       f"c.template local_arg<{is_max}>({value}));")
+                text, out_dtype = f"c.template xreduce_arg<{is_max}>({acc})", torch.int64
         elif reduction_type == "any":
             self.body.writeline(f"float {acc} = 0.f;")
             self.compute.writeline(f"{acc} = fmaxf({acc}, c.template local_fold<ixb::MaxOp>("

@@ -915,6 +915,61 @@ struct GenRowCtx : RowCtx<T, TEAM, TEAMS, VPT, false> {
     return xreduce_arg<IS_MAX>(local_arg<IS_MAX>(val));
   }
 
+  // arg-reductions of 32- and 64-bit integers: compared as integers (as floats, neighbours
+  // beyond 2^24 would tie and the smaller index would win); same tie rule, no NaN to consider
+  struct ArgPairI {
+    long long v, i;
+  };
+  template <bool IS_MAX> static __device__ __forceinline__ ArgPairI arg_identity_int() {
+    return ArgPairI{IS_MAX ? (-0x7fffffffffffffffLL - 1) : 0x7fffffffffffffffLL, 0x7fffffffffffffffLL};
+  }
+  template <bool IS_MAX> static __device__ __forceinline__ ArgPairI arg_better(ArgPairI a, ArgPairI b) {
+    const bool take_b = (a.v == b.v) ? (b.i < a.i) : (IS_MAX ? (b.v > a.v) : (b.v < a.v));
+    return take_b ? b : a;
+  }
+  template <bool IS_MAX, class A> __device__ __forceinline__ ArgPairI local_arg_int(const A& val) const {
+    ArgPairI best = arg_identity_int<IS_MAX>();
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < Base::kVec; ++j)
+        if (inside(i, j))
+          best = arg_better<IS_MAX>(
+              best, ArgPairI{Cast<long long>::from(at(val, i * Base::kVec + j)), (long long)(vec_col(i) + j)});
+    return best;
+  }
+  template <bool IS_MAX> __device__ __forceinline__ long long xreduce_arg_int(ArgPairI best) {
+#pragma unroll
+    for (int o = kGroup / 2; o > 0; o >>= 1) {
+      ArgPairI q;
+      q.v = __shfl_xor_sync(kFull, best.v, o);
+      q.i = __shfl_xor_sync(kFull, best.i, o);
+      best = arg_better<IS_MAX>(best, q);
+    }
+    if constexpr (kW > 1) {
+      long long* slot = reinterpret_cast<long long*>(slot_base());   // a slot holds the pair
+      if ((this->lane & 31) == 0) {
+        slot[(this->lane >> 5) * 2] = best.v;
+        slot[(this->lane >> 5) * 2 + 1] = best.i;
+      }
+      team_barrier(this->team + 1, TEAM);
+      best.v = slot[(this->lane & (kW - 1)) * 2];
+      best.i = slot[(this->lane & (kW - 1)) * 2 + 1];
+#pragma unroll
+      for (int o = kW / 2; o > 0; o >>= 1) {
+        ArgPairI q;
+        q.v = __shfl_xor_sync(kFull, best.v, o);
+        q.i = __shfl_xor_sync(kFull, best.i, o);
+        best = arg_better<IS_MAX>(best, q);
+      }
+      this->phase ^= 1;
+    }
+    return best.i;
+  }
+  template <bool IS_MAX, class A> __device__ __forceinline__ long long reduce_arg_int(const A& val) {
+    return xreduce_arg_int<IS_MAX>(local_arg_int<IS_MAX>(val));
+  }
+
   // ---- online softmax ------------------------------------------------------------------------
   // One exchange yields the row maximum, the sum of exp(value - maximum) and up to three
   // further row sums ("riders") that the emitter found it could form before the maximum is

@@ -361,3 +361,15 @@ def test_a_library_transformer_compiles_through_the_templates(dry_backend):
         code = generated(lambda input_ids: model(input_ids=input_ids)[0], ids)
     assert code.count("ixb_load_kernel(") >= 4 and "triton_" not in code
     assert "aten.native_dropout" in code or "aten.bernoulli" in code or "aten.rand" in code
+
+
+def test_integer_arg_reductions_compare_integers(dry_backend):
+    """argmax / argmin of int32 / int64 rows use the integer comparison (persistent and chunked
+    rows); narrower integers are exact in fp32 and keep the common path."""
+    big = (torch.arange(64 * 300).reshape(64, 300) % 7) + (1 << 40)
+    code = generated(lambda t: (t.argmax(-1), t.argmin(-1)), big)
+    assert "c.template reduce_arg_int<true>(" in code and "c.template reduce_arg_int<false>(" in code
+    code = generated(lambda t: t.argmax(-1), torch.randint(0, 1 << 40, (4, 70000)))
+    assert "c.template local_arg_int<true>(" in code and "c.template xreduce_arg_int<true>(" in code
+    code = generated(lambda t: t.argmin(-1), big.to(torch.uint8))
+    assert "c.template reduce_arg<false>(" in code

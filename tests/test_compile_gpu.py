@@ -781,3 +781,20 @@ def test_integer_pointwise_ops_match_eager(cuda):
     want = ((x[8:] * 3).to(torch.int32), (x[8:] * 3).to(torch.int64) // 2)
     for o, w in zip(got, want):
         assert torch.equal(o.cpu(), w)
+
+
+def test_integer_argmax_compares_integers(cuda):
+    """argmax / argmin of 64-bit integers whose differences vanish in fp32 (values near 2^40,
+    all distinct): the indices equal eager mode's, over the last axis, over the first axis and
+    over a row long enough to be walked in chunks."""
+    g = torch.Generator().manual_seed(15)
+    x = torch.randperm(37 * 1000, generator=g).reshape(37, 1000) + (1 << 40)
+    fn = lambda t: (t.argmax(-1), t.argmin(-1), t.argmax(0))
+    got, code = compile_and_code(fn, x.to(cuda))
+    assert "reduce_arg_int<true>(" in code and "reduce_arg_int<false>(" in code
+    for o, w in zip(got, fn(x)):
+        assert torch.equal(o.cpu(), w)
+    y = torch.randperm(3 * 70001, generator=g).reshape(3, 70001) + (1 << 40)
+    got, code = compile_and_code(lambda t: t.argmin(-1), y.to(cuda))
+    assert "xreduce_arg_int<false>(" in code
+    assert torch.equal(got.cpu(), y.argmin(-1))
