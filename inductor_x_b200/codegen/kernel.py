@@ -18,6 +18,7 @@ Loads and stores are classified by ``codegen/ir.py``: contiguous along the threa
 from __future__ import annotations
 
 import contextlib
+import math
 from typing import Any, Optional
 
 import sympy
@@ -411,7 +412,12 @@ class B200Kernel(SIMDKernel):
         idx = self.index_to_str(index)
         indirect = self._is_indirect(index)
         val_dtype = torch.float32 if dtype in FLOAT_DTYPES else (torch.bool if dtype == torch.bool else torch.int64)
-        other = "0" if self._load_other is None else constant_literal(self._load_other, val_dtype)
+        fill = self._load_other
+        if isinstance(fill, float) and val_dtype != torch.float32 and not math.isfinite(fill):
+            # a pad value of the converted result (max-pooling integers pads with -inf): the select
+            # after the masked sub-block supplies it, the load only needs some in-range value
+            fill = 0
+        other = "0" if fill is None else constant_literal(fill, val_dtype)
         other = {torch.float32: f"(float)({other})", torch.int64: f"(long long)({other})",
                  torch.bool: f"(bool)({other})"}[val_dtype]
         masked = self._load_mask is not None

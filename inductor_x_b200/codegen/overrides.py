@@ -43,6 +43,8 @@ def constant_literal(val, dtype: torch.dtype) -> str:
     if dtype == torch.bool:
         return "true" if val else "false"
     if dtype in INT_DTYPES:
+        if int(val) <= -(1 << 63):
+            return "(-9223372036854775807LL - 1)"      # the literal 9223372036854775808 has no signed type
         return f"{int(val)}LL"
     return float_literal(float(val))
 
@@ -109,6 +111,64 @@ class IxbExprPrinter(ExprPrinter):
 
     def _print_Identity(self, expr):
         return self.doprint(expr.args[0])
+
+    # ---- forms that appear with run-time extents (symbolic sizes) -----------------------
+    def _fn(self, name, expr):
+        return f"{OP}{name}({', '.join(self.doprint(a) for a in expr.args)})"
+
+    def _print_Mod(self, expr):                     # operands known non-negative
+        return self._fn("imod", expr)
+
+    def _print_PythonMod(self, expr):               # sign of the divisor, as Python's %
+        return self._fn("remainder", expr)
+
+    def _print_IntTrueDiv(self, expr):
+        a, b = (self.doprint(x) for x in expr.args)
+        return f"{OP}truediv({OP}to_float({a}), {OP}to_float({b}))"
+
+    def _print_FloatTrueDiv(self, expr):
+        return self._fn("truediv", expr)
+
+    def _print_FloatPow(self, expr):
+        return self._fn("pow", expr)
+
+    def _print_Rational(self, expr):
+        return float_literal(float(expr.p) / float(expr.q))
+
+    def _print_CeilToInt(self, expr):
+        return f"{OP}to_int({OP}ceil({self.doprint(expr.args[0])}))"
+
+    def _print_RoundToInt(self, expr):
+        return f"{OP}to_int({OP}round({self.doprint(expr.args[0])}))"
+
+    def _print_TruncToFloat(self, expr):
+        return self._fn("trunc", expr)
+
+    def _print_floor(self, expr):
+        return f"{OP}to_int({OP}floor({self.doprint(expr.args[0])}))"
+
+    def _print_ceiling(self, expr):
+        return f"{OP}to_int({OP}ceil({self.doprint(expr.args[0])}))"
+
+    def _print_Not(self, expr):
+        return self._fn("logical_not", expr)
+
+    def _print_BooleanTrue(self, expr):
+        return "true"
+
+    def _print_BooleanFalse(self, expr):
+        return "false"
+
+    def _print_Infinity(self, expr):
+        return "INFINITY"
+
+    def _print_NegativeInfinity(self, expr):
+        return "(-INFINITY)"
+
+
+for _fn_name in ("sqrt", "sin", "cos", "tan", "sinh", "cosh", "tanh", "asin", "acos", "atan", "log2"):
+    setattr(IxbExprPrinter, f"_print_OpaqueUnaryFn_{_fn_name}",
+            (lambda name: lambda self, expr: self._fn(name, expr))(_fn_name))
 
 
 def _call(name):

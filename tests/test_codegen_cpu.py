@@ -373,3 +373,25 @@ def test_integer_arg_reductions_compare_integers(dry_backend):
     assert "c.template local_arg_int<true>(" in code and "c.template xreduce_arg_int<true>(" in code
     code = generated(lambda t: t.argmin(-1), big.to(torch.uint8))
     assert "c.template reduce_arg<false>(" in code
+
+
+def test_symbolic_extents_print_python_mod_and_true_division(dry_backend):
+    """Forms that only appear with run-time extents: Python's modulo (a rolled index) and the
+    true division of two extents (the n / (n - 1) factor of a batch-norm's running variance)."""
+    import torch._dynamo
+
+    def compiled_dynamic(fn, *args):
+        from torch._inductor.utils import run_and_get_code
+
+        torch._dynamo.reset()
+        _, code = run_and_get_code(torch.compile(fn, dynamic=True), *args)
+        return "\n".join(code)
+
+    code = compiled_dynamic(lambda t: t.roll(3, -1) + 1, torch.randn(4, 64))
+    assert "ixb::gen::op::remainder(" in code and "ixb_load_kernel(" in code
+    bn = torch.nn.BatchNorm2d(16).train()
+    code = compiled_dynamic(bn, torch.randn(8, 16, 14, 14))
+    assert "ixb::gen::op::truediv(ixb::gen::op::to_float(" in code and "triton_" not in code
+    # a non-finite pad value behind an integer load (max-pooling integers converted to float)
+    code = generated(lambda a: F.max_pool1d(a.view(1, 1, 100).float(), 3, 1, 1), torch.randint(1, 10, (100,)))
+    assert "ixb_load_kernel(" in code
