@@ -15,22 +15,6 @@ import torch.nn.functional as F
 pytestmark = pytest.mark.skipif(shutil.which("nvcc") is None, reason="nvcc not available")
 
 
-@pytest.fixture(scope="module")
-def dry_backend(tmp_path_factory):
-    """The backend registered for CPU tensors in dry-run mode: sources are emitted and built
-    with nvcc exactly as on a GPU, nothing is launched."""
-    os.environ["IXB_CACHE_DIR"] = str(tmp_path_factory.mktemp("ixbcache"))
-    import inductor_x_b200
-    from inductor_x_b200 import config
-    from inductor_x_b200.prebuild import _dry_cpu_backend
-
-    old_dir = config.cache_dir
-    config.cache_dir = os.environ["IXB_CACHE_DIR"]
-    with _dry_cpu_backend(False):
-        yield
-    config.cache_dir = old_dir
-
-
 def launch_shape(code):
     """(team, teams, vpt) a generated row module names as its default launch shape."""
     return tuple(int(re.search(rf"#define IXB_ROW_{m} (\d+)", code).group(1)) for m in ("TEAM", "TEAMS", "VPT"))
