@@ -4,7 +4,8 @@ test_AddLayerNorm.py), restated with the same operators, dtypes and - where they
 the same shapes.  Each script compiles a function with the Inductor backend and compares with
 eager mode at rtol = atol = 1e-3; the GPU tests here do the same through this backend (with the
 tolerance tightened to what fp32 / fp16 arithmetic gives), and the CPU test checks that every
-graph is instantiated from the templates without a Triton kernel."""
+graph is instantiated from the templates without a Triton kernel.  Collected last so that a
+failure here cannot mask other tests."""
 import pytest
 import torch
 import torch.nn.functional as F
