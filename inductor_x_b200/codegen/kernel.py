@@ -223,11 +223,16 @@ class B200Kernel(SIMDKernel):
         always use the outer mapping, whose body loops over the reduced axis anyway."""
         if not self.features.is_reduction():
             return True
+        vec = min(max(ixb_config.get_aligned_numel(self._narrowest_node_dtype()), 1), 8)
         try:
             rnumel = int(self.features.reduction_numel)
         except TypeError:
-            return True                  # run-time extent: persistent up to the compiled capacity
-        vec = min(max(ixb_config.get_aligned_numel(self._narrowest_node_dtype()), 1), 8)
+            # run-time extent: persistent up to the compiled capacity; where the extent seen at
+            # trace time is beyond what any launch shape holds, the row is walked in chunks, whose
+            # count the launcher derives from the run-time extent (any length is served)
+            hint = int(V.graph.sizevars.size_hint(self.features.reduction_numel))
+            self.looped = -(-hint // vec) > split_tiling.MAX_TEAM * split_tiling.MAX_VPT
+            return not self.looped
         nvec = -(-rnumel // vec)
         long_row = nvec > split_tiling.MAX_TEAM * split_tiling.MAX_PERSISTENT_VPT
         try:

@@ -379,3 +379,17 @@ def test_symbolic_extents_print_python_mod_and_true_division(dry_backend):
     # a non-finite pad value behind an integer load (max-pooling integers converted to float)
     code = generated(lambda a: F.max_pool1d(a.view(1, 1, 100).float(), 3, 1, 1), torch.randint(1, 10, (100,)))
     assert "ixb_load_kernel(" in code
+
+
+def test_long_rows_of_run_time_length_are_walked_in_chunks(dry_backend):
+    """A symbolic reduced extent whose trace-time value is beyond every launch shape (a full
+    reduction of a tensor with run-time sizes, a very long softmax row) becomes the chunked row
+    kernel: the chunk count comes from the extent the launcher passes, so any length is served."""
+    from torch._inductor.utils import run_and_get_code
+
+    for fn, x in ((lambda t: t.sum(), torch.randn(1000, 1000)), (lambda t: t.softmax(-1), torch.randn(4, 200000))):
+        torch._dynamo.reset()
+        _, code = run_and_get_code(torch.compile(fn, dynamic=True), x)
+        code = "\n".join(code)
+        assert "static constexpr bool kLooped = true;" in code and "c.nchunks()" in code
+        assert "long long r_extent;" in code and "(int)r_extent" in code

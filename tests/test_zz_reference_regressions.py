@@ -173,3 +173,15 @@ def test_regression_graphs_match_eager(cuda, name):
         else:
             scale = max(w.float().abs().max().item(), 1.0)
             assert (o.float() - w.float()).abs().max().item() <= tol * scale, name
+
+
+@pytest.mark.gpu
+def test_full_reduction_with_run_time_sizes(cuda):
+    """A loss-style mean over every element of a tensor whose sizes are symbolic: one chunked row
+    kernel serves both sizes (the launcher passes the reduced extent)."""
+    g = torch.Generator().manual_seed(58)
+    fn = torch.compile(lambda t: (t * t).mean(), dynamic=True)
+    for shape in ((1000, 1024), (1500, 900), (64, 100)):
+        x = torch.randn(*shape, generator=g).to(cuda)
+        want = (x.double() * x.double()).mean()
+        assert abs(fn(x).double().item() - want.item()) <= 1e-5 * abs(want.item())
