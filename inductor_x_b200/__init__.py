@@ -98,6 +98,17 @@ def _route_random_ops_to_aten():
     inductor_config.fallback_random = True
 
 
+def _specialize_python_floats():
+    """Python ``float`` arguments of a compiled function are baked into the graph as constants
+    (Dynamo's ``specialize_float``; a new value recompiles).  Left symbolic, such a float enters
+    the graph as a 0-dim float64 host tensor - with ``dynamic=True`` that happens to the softmax
+    scale or the rotary scaling factor of library models - and generated kernels take device
+    pointers and integer scalars only, and no float64."""
+    import torch._dynamo.config as dynamo_config
+
+    dynamo_config.specialize_float = True
+
+
 def register():
     """Perform the registrations (idempotent).  Called at import unless IXB_REGISTER=0."""
     global _registered
@@ -111,6 +122,7 @@ def register():
     _register_device_interface()
     _enable_online_softmax_pattern()
     _route_random_ops_to_aten()
+    _specialize_python_floats()
     from .codegen.ir import install_num_splits
 
     install_num_splits()

@@ -57,9 +57,18 @@ class GeneratedKernel:
         self.path = path
 
     def run(self, *args, stream=None):
-        ptrs, ints = [], []
+        ptrs, ints, keep = [], [], []
         for a in args:
             if isinstance(a, torch.Tensor):
+                if not (a.is_cuda or config.dry_run):
+                    # a host tensor: its address means nothing on the device.  A single element
+                    # (eager mode lets a 0-dim host tensor meet device tensors) is copied over,
+                    # ordered on the current stream; anything larger is a caller's mistake.
+                    if a.numel() != 1:
+                        raise RuntimeError(f"generated kernel {self.meta.get('name', self.key)}: argument of "
+                                           f"shape {tuple(a.shape)} lives on {a.device}, not on a CUDA device")
+                    a = a.to(torch.device("cuda", torch.cuda.current_device()))
+                    keep.append(a)
                 ptrs.append(a.data_ptr())
             else:
                 ints.append(int(a))

@@ -393,3 +393,14 @@ def test_long_rows_of_run_time_length_are_walked_in_chunks(dry_backend):
         code = "\n".join(code)
         assert "static constexpr bool kLooped = true;" in code and "c.nchunks()" in code
         assert "long long r_extent;" in code and "(int)r_extent" in code
+
+
+def test_python_float_arguments_are_baked_into_the_graph(dry_backend):
+    """With dynamic shapes a Python float would enter the graph as a 0-dim float64 host tensor;
+    registration specialises floats instead, so the scale is a literal of the generated kernel."""
+    from torch._inductor.utils import run_and_get_code
+
+    torch._dynamo.reset()
+    _, code = run_and_get_code(torch.compile(lambda t, s: t * s + 1, dynamic=True), torch.randn(64, 100), 0.37)
+    code = "\n".join(code)
+    assert "0.37f" in code and "double" not in code.split("extern \"C\"")[0].split("struct Body")[1]
