@@ -404,3 +404,28 @@ def test_python_float_arguments_are_baked_into_the_graph(dry_backend):
     _, code = run_and_get_code(torch.compile(lambda t, s: t * s + 1, dynamic=True), torch.randn(64, 100), 0.37)
     code = "\n".join(code)
     assert "0.37f" in code and "double" not in code.split("extern \"C\"")[0].split("struct Body")[1]
+
+
+def test_integer_range_helpers():
+    """Host logic behind the integer wrap: which conversions can leave the target's range and
+    how a wrap is printed."""
+    import inductor_x_b200  # noqa: F401
+    from inductor_x_b200.codegen.overrides import _fits, _narrow_int_result, _wrap
+
+    assert _fits(torch.uint8, torch.int16) and _fits(torch.int8, torch.int32) and _fits(torch.bool, torch.uint8)
+    assert _fits(torch.int32, torch.int64) and _fits(torch.int16, torch.int16)
+    assert not _fits(torch.int64, torch.int32) and not _fits(torch.int8, torch.uint8)      # sign is lost
+    assert not _fits(torch.uint8, torch.int8) and not _fits(torch.float32, torch.int64)
+    assert _wrap("v", torch.int64) == "v" and _wrap("v", torch.bool) == "v" and _wrap("v", None) == "v"
+    assert _wrap("v", torch.uint8) == "ixb::gen::op::wrap_int<8, false>(v)"
+    assert _wrap("v", torch.int16) == "ixb::gen::op::wrap_int<16, true>(v)"
+
+    class Val:
+        def __init__(self, dtype, int_type=None):
+            self.dtype, self.int_type = dtype, int_type
+
+    i32, u8, i64 = Val(torch.int64, torch.int32), Val(torch.int64, torch.uint8), Val(torch.int64)
+    assert _narrow_int_result(i32, 3) == torch.int32                 # Python scalars do not promote
+    assert _narrow_int_result(i32, u8) == torch.int32 and _narrow_int_result(u8, Val(torch.bool)) == torch.uint8
+    assert _narrow_int_result(i32, i64) is None                      # 64-bit results need no wrap
+    assert _narrow_int_result(i32, Val(torch.float32)) is None       # not an integer result
