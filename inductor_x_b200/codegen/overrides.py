@@ -450,7 +450,9 @@ for _name in ["exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "
     setattr(B200Overrides, _name, _call(_name))
 for _name in ["add", "sub", "mul", "truediv", "exp"]:
     setattr(B200Overrides, _name, staticmethod(getattr(_Peephole, _name)))
-B200Overrides.neg = staticmethod(lambda a: _wrap(f"{OP}neg({a})", _narrow_int_result(a)))
+for _name in ("neg", "abs", "square"):        # -x, |x| and x * x of the most negative value leave the range too
+    setattr(B200Overrides, _name,
+            staticmethod((lambda n: lambda a: _wrap(f"{OP}{n}({a})", _narrow_int_result(a)))(_name)))
 B200Overrides.mod = _call("mod")
 B200Overrides.fma = _call("fma")
 B200Overrides.mul_rn = _call("mul")       # a product that is never contracted: its name keeps it out of the fma peephole
